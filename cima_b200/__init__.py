@@ -14,12 +14,14 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Union
 
-from .config import (ArchitectureEntry, ConfigError, Qwen2Config, lookup_architecture, read_config_json,
+from .config import (ArchitectureEntry, ConfigError, Qwen2Config, VunovikConfig, lookup_architecture, read_config_json,
                      register_architecture, registered_architectures)
 from .sampling import GenOptions, OptionError
 
 register_architecture(ArchitectureEntry(name=Qwen2Config.ARCHITECTURE, model_type="qwen2",
                                         parse=Qwen2Config.from_dict, spec=Qwen2Config.model_spec))
+register_architecture(ArchitectureEntry(name=VunovikConfig.ARCHITECTURE, model_type="vunovik",
+                                        parse=VunovikConfig.from_dict, spec=VunovikConfig.model_spec))
 
 __version__ = "0.1.0"
 
@@ -135,5 +137,5 @@ def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int 
 
 
 __all__ = ["LM", "load", "write_random_model", "eos_ids_of", "GenOptions", "OptionError", "ConfigError",
-           "Qwen2Config", "register_architecture", "registered_architectures", "lookup_architecture",
+           "Qwen2Config", "VunovikConfig", "register_architecture", "registered_architectures", "lookup_architecture",
            "read_config_json", "ArchitectureEntry"]

@@ -1,8 +1,8 @@
 """The cache: a slot for each live sequence, keys and values for each layer in pages, and
 fixed-size state for each slot beside them.
 
-Layout.  Layers whose mixers ask for the same storage (KV heads, head size, window) form a
-*group*.  A group owns ``[layers, pages, 2 (k|v), kv_heads, page_size, head_dim]`` and one block
+Layout.  Layers whose mixers ask for the same storage (KV heads, head size, window, planes) form a
+*group*.  A group owns ``[layers, pages, planes (k|v, or one shared), kv_heads, page_size, head_dim]`` and one block
 table ``[slots, width]`` of page ids that all its layers share.  A group that keeps every key
 gives a sequence one page per ``page_size`` positions; a group with a window of ``w`` keys gives
 it a ring of ``ceil(w / page_size) + 1`` pages, position ``p`` living in ring entry
@@ -29,10 +29,13 @@ from .pages import CacheFull, FreeList
 @dataclass(frozen=True)
 class KVRequest:
     """What a mixer needs per position: keys and values of ``n_kv_heads`` heads of ``head_dim``;
-    ``window`` 0 = all positions are kept, w > 0 = only the last w need to be."""
+    ``window`` 0 = all positions are kept, w > 0 = only the last w need to be.  ``planes`` 2 = keys and values
+    are kept apart; 1 = one vector per position and head serves as both (a latent that the mixer projects
+    keys and values from)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -50,12 +53,13 @@ class CapacityError(RuntimeError):
 @dataclass
 class LayerKV:
     """What an attention kernel needs to find a layer's keys and values."""
-    storage: torch.Tensor        # [pages, 2, kv_heads, page_size, head_dim] of this layer
+    storage: torch.Tensor        # [pages, planes (k|v, or 1), kv_heads, page_size, head_dim] of this layer
     block_table: torch.Tensor    # [slots, width] int32, shared by the group
     page_size: int
     ring_pages: int              # 0 = one table entry per page of positions; R = ring of R entries
     window: int
     group: int
+    planes: int = 2
 
 
 class KVGroup:
@@ -72,7 +76,9 @@ class KVGroup:
         self.pages_of: List[List[int]] = [[] for _ in range(n_slots)]
         self.table_host = np.zeros((n_slots, self.width), dtype=np.int32)
         self.block_table = torch.zeros((n_slots, self.width), dtype=torch.int32, device=device)
-        self.storage = torch.zeros((len(layers), n_pages, 2, request.n_kv_heads, page_size, request.head_dim),
+        if request.planes not in (1, 2):
+            raise ValueError(f"a cache request has {request.planes} planes; 2 (keys | values) or 1 (shared) are possible")
+        self.storage = torch.zeros((len(layers), n_pages, request.planes, request.n_kv_heads, page_size, request.head_dim),
                                    dtype=dtype, device=device)
         self.dirty: set = set()
 
@@ -183,7 +189,7 @@ class KVCache:
         gi, li = self._layer_group[layer]
         g = self.groups[gi]
         return LayerKV(storage=g.storage[li], block_table=g.block_table, page_size=self.page_size,
-                       ring_pages=g.ring_pages, window=g.request.window, group=gi)
+                       ring_pages=g.ring_pages, window=g.request.window, group=gi, planes=g.request.planes)
 
     def most_tokens_going_on(self) -> Optional[int]:
         """The most tokens that a sequence which already holds positions may add in one step whose rows read the

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to what builds its model.
 
 The name is ``architectures[0]`` of config.json (``model_type`` as a second
-key).  The reference plays this role with an allowlist of model types and a
+key), or the single name under ``architecture`` where a design writes it so.  The reference plays this role with an allowlist of model types and a
 closed enum of resident graphs (src/models/transformer.rs:113-153,
 src/models/mod.rs:215-275); here it is an open table, so that another
 architecture is one ``register_architecture`` call.
@@ -44,6 +44,8 @@ def registered_architectures():
 def lookup_architecture(raw_config: Dict[str, Any]) -> ArchitectureEntry:
     """The entry for a config.json dict; unknown names fail with the list of known ones."""
     archs = raw_config.get("architectures")
+    if archs is None and isinstance(raw_config.get("architecture"), str):
+        archs = [raw_config["architecture"]]
     if isinstance(archs, list):
         for a in archs:
             if a in _BY_NAME:

@@ -64,15 +64,27 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class ShortConvSpec:
+    """A causal convolution over time on each channel, added to its input: u_t = h_t + sum_j w[:, j] h_(t-taps+1+j),
+    nothing before position 0.  A sequence carries its newest ``taps - 1`` inputs along as state."""
+    channels: int
+    taps: int
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     kind: str                    # "prenorm": x += mixer(norm(x)); x += ffn(norm(x))
+                                 # "parallel": h = norm(x); x += mixer(conv(h)) + ffn(h)
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]      # None: the layer has no feed-forward ("parallel" only)
     mixer_norm: NormSpec
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]                 # None where one norm serves both sublayers
     prefix: str                  # tensor-name prefix of the layer, e.g. "model.layers.3."
-    # tensor-name stems under the prefix, owned by the architecture's naming
+    # tensor-name stems under the prefix, owned by the architecture's naming; a matrix or norm weight is
+    # prefix + stem + names.get("suffix", ".weight")
     names: Dict[str, str] = field(default_factory=dict)
+    # a short convolution in front of the mixer (its weight's stem is names["mixer_conv"]); None = none
+    mixer_conv: Optional[ShortConvSpec] = None
 
 
 @dataclass(frozen=True)
@@ -97,10 +109,15 @@ class ModelSpec:
     # Prefixes of the tensor names above that a checkpoint may leave out (a bare backbone stores
     # "layers.0..." for "model.layers.0..."; the reference tries both, src/models/transformer.rs:472-488).
     optional_prefixes: Tuple[str, ...] = ()
+    # What a layer reads.  "residual": the stream as the layer before left it.  "depth_average": with X_0 the
+    # embedding's output and X_(s+1) the stream as site s leaves it, the next site (and the final norm) reads
+    # sum_(j <= s+1) a_s[j] X_j; ``depth_names[s]`` names the vector a_s (s + 2 values) of site s.
+    stream: str = "residual"
+    depth_names: Tuple[str, ...] = ()
 
     def describe(self) -> str:
         kinds = [f"{self.layers[i].mixer.kind}"
                  f"{'(w=%d)' % self.layers[i].mixer.window if self.layers[i].mixer.window else ''}"
-                 f"+{self.layers[i].feed_forward.kind}" for i in self.schedule]
+                 f"+{self.layers[i].feed_forward.kind if self.layers[i].feed_forward else 'none'}" for i in self.schedule]
         return (f"{self.architecture}: vocab {self.vocab}, hidden {self.hidden}, "
                 f"{len(self.layers)} layers, schedule {kinds}")

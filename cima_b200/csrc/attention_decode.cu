@@ -120,14 +120,15 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   };
   auto issue = [&](int page, int stage) {
     // one page: K then V, each [PS][HD] contiguous in the cache -> padded rows in shared memory
-    const __nv_bfloat16* src = cache + (((size_t)page * 2) * pg.kv_heads + kvh) * (size_t)(PS * HD);
+    // (with one plane the page's vectors are keys and values at once: one copy, and the V tile is the K tile)
+    const __nv_bfloat16* src = cache + (((size_t)page * pg.planes) * pg.kv_heads + kvh) * (size_t)(PS * HD);
     const size_t vofs = (size_t)pg.kv_heads * PS * HD;
     __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
     for (int c = threadIdx.x; c < PS * CPR; c += WARPS * 32) {
       const int r = c / CPR, cc = c % CPR;
       cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
-      cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+      if (pg.planes == 2) cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
     }
   };
 
@@ -179,7 +180,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     cp_async_commit();
     if (p + STAGES < p1) page_next = page_of(p + STAGES);
     const __nv_bfloat16* Kt = tiles + (size_t)stage * 2 * TILE;
-    const __nv_bfloat16* Vt = Kt + TILE;
+    const __nv_bfloat16* Vt = pg.planes == 2 ? Kt + TILE : Kt;
     const int kw = warp * KEYS_PER_WARP;              // this warp's keys within the page
 
     // S = Q K^T for 16 keys: two n-tiles of 8 keys
@@ -378,15 +379,16 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
 extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, float* part_o,
                                      float* part_ml, void* out, int ldo, int B, int nh, int nkv, int hd, float scale,
-                                     int window, int n_splits, int early, cudaStream_t stream) {
+                                     int window, int n_splits, int early, int planes, cudaStream_t stream) {
   if (B <= 0) return 0;
+  if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_decode: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (page_size != PS) return cima_fail(CIMA_E_SIZE, "attention_decode: page size %d; this kernel takes 64", page_size);
   if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d; this kernel takes multiples of 16 up to 128", hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
   if (n_splits < 1 || n_splits > MAX_SPLITS || B > 65535) return cima_fail(CIMA_E_SIZE, "attention_decode: %d splits / %d sequences exceed one launch", n_splits, B);
   if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
   if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
-  CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+  CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
 #define CASE(H) case H: return launch_decode<H>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
@@ -442,5 +444,5 @@ extern "C" int cima_attention_decode_static(const void* qkv, int ld, const void*
   float* part_o = scratch;                       // [B, nh, n_splits, hd]
   float* part_ml = scratch + cells * hd;         // [B, nh, n_splits, 2]
   return cima_attention_decode(qkv, ld, cache, table, table_width, ring, page_size, seq_slot, seq_len, part_o, part_ml,
-                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, stream);
+                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, 2, stream);
 }

@@ -9,7 +9,7 @@
 // A row's result depends only on its own sequence: same bits alone or in any batch.
 #include "common.cuh"
 
-template <typename TA, bool FROM_CACHE>
+template <typename TA, bool FROM_CACHE, int NI>       // NI: values of a head per lane (head_dim <= 32 NI)
 __global__ void __launch_bounds__(128)
 k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cache, CimaPaged pg,
                   const int* __restrict__ row_pos, const int* __restrict__ row_seq,
@@ -27,10 +27,10 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
   const int first = FROM_CACHE ? 0 : seq_first_row[seq];
   const int kcol = (nh + kvh) * hd, vcol = (nh + nkv + kvh) * hd;
 
-  float q[8], acc[8];
+  float q[NI], acc[NI];
   const TA* qp = qkv + (size_t)row * ld + (size_t)h * hd;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
+  for (int i = 0; i < NI; i++) {
     const int d = lane + 32 * i;
     q[i] = d < hd ? cima_to_f32<TA>(qp[d]) : 0.f;
     acc[i] = 0.f;
@@ -48,7 +48,7 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
     }
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < NI; i++) {
       const int d = lane + 32 * i;
       if (d < hd) s = fmaf(q[i], cima_to_f32<TA>(kp[d]), s);
     }
@@ -58,7 +58,7 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
     const float m2 = fmaxf(m, s);
     const float corr = expf(m - m2), p = expf(s - m2);
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < NI; i++) {
       const int d = lane + 32 * i;
       if (d < hd) acc[i] = acc[i] * corr + p * cima_to_f32<TA>(vp[d]);
     }
@@ -68,7 +68,7 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
   TA* op = out + (size_t)row * ldo + (size_t)h * hd;
   const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
+  for (int i = 0; i < NI; i++) {
     const int d = lane + 32 * i;
     if (d < hd) op[d] = cima_from_f32<TA>(acc[i] * inv);
   }
@@ -79,19 +79,22 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
                                     int table_width, int ring, int page_size, const int* row_pos,
                                     const int* row_seq, const int* seq_slot, const int* seq_first_row, void* out,
                                     int ldo, int T, int nh, int nkv, int hd, float scale, int window,
-                                    int from_cache, cudaStream_t stream) {
+                                    int from_cache, int planes, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd > 256) return cima_fail(CIMA_E_SIZE, "attention_plain: head_dim %d is outside 1..256", hd);
+  if (hd <= 0 || hd > 1024) return cima_fail(CIMA_E_SIZE, "attention_plain: head_dim %d is outside 1..1024", hd);
+  if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_plain: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_plain: %d heads are not a multiple of %d kv heads", nh, nkv);
   if (nh > 65535) return cima_fail(CIMA_E_SIZE, "attention_plain: %d heads exceed one launch", nh);
   if (from_cache && (!cache || !table)) return cima_fail(CIMA_E_ARG, "attention_plain: decoding needs the cache and its block table");
-  CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+  CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
   dim3 grid((T + 3) / 4, nh);
-#define LAUNCH(TA, FC) { int rc_ = cima_launch(k_attention_plain<TA, FC>, dim3(grid), dim3(128), (size_t)(0), stream, 1, (const TA*)qkv, ld, (const TA*)cache, pg, \
-    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window); if (rc_) return rc_; }
+#define LAUNCH(TA, FC) { int rc_ = hd <= 256 ? LAUNCH_NI(TA, FC, 8) : LAUNCH_NI(TA, FC, 32); if (rc_) return rc_; }
+#define LAUNCH_NI(TA, FC, NI) cima_launch(k_attention_plain<TA, FC, NI>, dim3(grid), dim3(128), (size_t)(0), stream, 1, (const TA*)qkv, ld, (const TA*)cache, pg, \
+    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window)
   if (dtype == CIMA_F32) { if (from_cache) LAUNCH(float, true) else LAUNCH(float, false) }
   else if (dtype == CIMA_BF16) { if (from_cache) LAUNCH(__nv_bfloat16, true) else LAUNCH(__nv_bfloat16, false) }
   else return cima_fail(CIMA_E_DTYPE, "attention_plain: dtype code %d is neither float32 nor bfloat16", dtype);
 #undef LAUNCH
+#undef LAUNCH_NI
   return cima_launch_result();
 }

@@ -122,8 +122,8 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
       int e = kt;
       if (pg.ring) e %= pg.ring;
       const int page = pg.table[(size_t)slot * pg.width + e];
-      const __nv_bfloat16* src = cache + (((size_t)page * 2) * pg.kv_heads + kvh) * (size_t)(BN * HD);
-      const size_t vofs = (size_t)pg.kv_heads * BN * HD;
+      const __nv_bfloat16* src = cache + (((size_t)page * pg.planes) * pg.kv_heads + kvh) * (size_t)(BN * HD);
+      const size_t vofs = pg.planes == 2 ? (size_t)pg.kv_heads * BN * HD : 0;      // one plane: the values are the keys
       for (int c = threadIdx.x; c < BN * CPR; c += WARPS * 32) {
         const int r = c / CPR, cc = c % CPR;
         cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
@@ -318,12 +318,13 @@ extern "C" int cima_attention_extend(const void* qkv, int ld, const int* tile_se
                                      const int* seq_first_row, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, void* out, int ldo,
                                      int T, int n_tiles, int nh, int nkv, int hd, float scale, int window,
-                                     cudaStream_t stream) {
+                                     int planes, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
+  if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_extend: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
   if (int rc = prefill_checks("attention_extend", qkv, ld, out, ldo, hd, nh, nkv)) return rc;
   if (page_size != BN) return cima_fail(CIMA_E_SIZE, "attention_extend: page size %d; this kernel takes %d", page_size, BN);
   if (!cache || !table || !seq_slot || !seq_len || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_extend: the cache (16-byte aligned), its block table, slots and lengths are needed");
-  const CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+  const CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
 #define CASE(H) case H: return launch_prefill<H, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, cache, pg, seq_slot, seq_len, out, ldo, T, n_tiles, nh, nkv, scale, window, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);

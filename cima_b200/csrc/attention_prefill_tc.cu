@@ -59,6 +59,7 @@ struct AttnArgs {
   int ldo, nh, nkv, window;
   float scale;
   int* error_flag;
+  int planes;                   // keys from the cache: 2 = a page holds keys, then values; 1 = one vector serves as both
 };
 
 // Keys of a query block whose rows stand at positions p0 .. (at most p0 + 127, below len): tiles [first, last] of 64.
@@ -146,7 +147,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         if (j >= 2 && !mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
         mbar_expect_tx(&k_full[s], NH * KHALF_BYTES);
         // from the cache, map_k covers the layer's pages as rows of head_dim values: page, k or v, kv head, position
-        const int x = FROM_CACHE ? 0 : (a.nh + kvh) * HD, y = FROM_CACHE ? (page_of(first + j) * 2 * a.nkv + kvh) * BN : row_base + k0;
+        const int x = FROM_CACHE ? 0 : (a.nh + kvh) * HD, y = FROM_CACHE ? (page_of(first + j) * a.planes * a.nkv + kvh) * BN : row_base + k0;
 #pragma unroll
         for (int kb = 0; kb < NH; kb++)
           tma_load_2d(sk + (size_t)(NH * s + kb) * KHALF_BYTES, &map_k, x + 64 * kb, y, &k_full[s]);
@@ -157,7 +158,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         if (j >= 2 && !mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
         mbar_expect_tx(&v_full[s], V_BYTES);
         const int x = FROM_CACHE ? 0 : (a.nh + a.nkv + kvh) * HD;
-        const int y = FROM_CACHE ? ((page_of(first + j) * 2 + 1) * a.nkv + kvh) * BN : row_base + k0;
+        const int y = FROM_CACHE ? ((page_of(first + j) * a.planes + (a.planes - 1)) * a.nkv + kvh) * BN : row_base + k0;
 #pragma unroll
         for (int kb = 0; kb < NH; kb++)
           tma_load_2d(sv + (size_t)s * V_BYTES + (size_t)kb * KHALF_BYTES, &map_k, x + 64 * kb, y, &v_full[s]);
@@ -348,6 +349,7 @@ struct CacheSource {              // keys and values from a layer's pages; cache
   long long n_pages;
   const int *table, *seq_slot, *seq_len;
   int table_width, ring;
+  int planes = 2;
 };
 
 template <int HD, bool FROM_CACHE>
@@ -356,9 +358,10 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
                         int window, int* error_flag, cudaStream_t stream) {
   if ((long long)n_tiles * nh > 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d blocks of rows x %d heads exceed one launch", n_tiles, nh);
   CUtensorMap mq, mk;                                  // boxes of 128 rows (Q) and of 64 rows (K and V) by 64 columns
-  int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * HD, ld);
+  // (with the keys in the cache only the queries' columns of a row are read, and the row may end there)
+  int rc = make_map(&mq, qkv, T, FROM_CACHE ? (long long)nh * HD : (long long)(nh + 2 * nkv) * HD, ld);
   if (rc) return rc;
-  if (FROM_CACHE) rc = make_map(&mk, c.cache, c.n_pages * 2 * nkv * BN, HD, HD, BN);
+  if (FROM_CACHE) rc = make_map(&mk, c.cache, c.n_pages * c.planes * nkv * BN, HD, HD, BN);
   else rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * HD, ld, BN);
   if (rc) return rc;
   constexpr int NH = HD / 64;
@@ -371,18 +374,19 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
     raised = true;
   }
   AttnArgs a{tile_seq, tile_row0, seq_first_row, c.seq_len, c.seq_slot, c.table, c.table_width, c.ring,
-             (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
+             (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag, c.planes};
   { int rc_ = cima_launch(k_attention_prefill_tc<HD, FROM_CACHE>, dim3((unsigned)n_tiles * (unsigned)nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
 }  // namespace
 
-static int tc_checks(const char* who, const void* qkv, int ld, const void* out, int ldo, int nh, int nkv, int hd, const int* error_flag) {
+static int tc_checks(const char* who, const void* qkv, int ld, const void* out, int ldo, int nh, int nkv, int hd, const int* error_flag,
+                     bool queries_only = false) {
   if (hd != 64 && hd != 128) return cima_fail(CIMA_E_SIZE, "%s: head_dim %d; this kernel takes 64 or 128", who, hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "%s: %d heads are not a multiple of %d kv heads", who, nh, nkv);
   if (ld % 8 || ldo % 8) return cima_fail(CIMA_E_SIZE, "%s: row strides (%d, %d) must be multiples of 8", who, ld, ldo);
-  if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "%s: row stride %d is smaller than (heads + 2 kv heads) * head_dim", who, ld);
+  if (ld < (queries_only ? nh : nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "%s: row stride %d is smaller than the heads of a row", who, ld);
   if ((((uintptr_t)qkv | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "%s: qkv and out must be 16-byte aligned", who);
   if (!error_flag) return cima_fail(CIMA_E_ARG, "%s: an error flag on the device is needed", who);
   if (nh > 65535 || nkv > 65535) return cima_fail(CIMA_E_SIZE, "%s: %d heads exceed one launch", who, nh);
@@ -404,19 +408,20 @@ extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* til
 }
 
 // The same for sequences that go on: the rows of sequence s are the positions seq_len[s] - rows .. seq_len[s] - 1, and
-// every key, the step's own included, is read from the layer's pages: cache [n_pages, 2, nkv, 64, head_dim] bf16.
+// every key, the step's own included, is read from the layer's pages: cache [n_pages, planes, nkv, 64, head_dim] bf16.
 extern "C" int cima_attention_extend_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
                                         const int* seq_first_row, const void* cache, long long n_pages, const int* table,
                                         int table_width, int ring, int page_size, const int* seq_slot, const int* seq_len,
                                         void* out, int ldo, int T, int n_tiles, int nh, int nkv, int hd, float scale,
-                                        int window, int* error_flag, cudaStream_t stream) {
+                                        int window, int* error_flag, int planes, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
-  if (int rc = tc_checks("attention_extend_tc", qkv, ld, out, ldo, nh, nkv, hd, error_flag)) return rc;
+  if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_extend_tc: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
+  if (int rc = tc_checks("attention_extend_tc", qkv, ld, out, ldo, nh, nkv, hd, error_flag, true)) return rc;
   if (page_size != BN) return cima_fail(CIMA_E_SIZE, "attention_extend_tc: page size %d; this kernel takes %d", page_size, BN);
   if (!cache || !table || !seq_slot || !seq_len || ((uintptr_t)cache & 15) || n_pages <= 0)
     return cima_fail(CIMA_E_ARG, "attention_extend_tc: the cache (16-byte aligned), its block table, slots and lengths are needed");
-  if (n_pages * 2 * nkv * BN >= (1ll << 31)) return cima_fail(CIMA_E_SIZE, "attention_extend_tc: %lld pages exceed a tensor map's 32-bit row coordinate", n_pages);
-  const CacheSource c{cache, n_pages, table, seq_slot, seq_len, table_width, ring};
+  if (n_pages * planes * nkv * BN >= (1ll << 31)) return cima_fail(CIMA_E_SIZE, "attention_extend_tc: %lld pages exceed a tensor map's 32-bit row coordinate", n_pages);
+  const CacheSource c{cache, n_pages, table, seq_slot, seq_len, table_width, ring, planes};
   if (hd == 64)
     return launch_attention_tc<64, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
   return launch_attention_tc<128, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);

@@ -78,7 +78,9 @@ __device__ __forceinline__ float cima_block_max(float v, float* red) {
 }
 
 // Where position `pos` of slot `slot` lives in a layer's paged keys/values.
-// storage: [pages][2][kv_heads][page_size][head_dim]; table: [slots][width].
+// storage: [pages][planes][kv_heads][page_size][head_dim]; table: [slots][width].  planes 2: keys, then values;
+// planes 1: one vector per position and head is both key and value (a latent), and asking for the values
+// (kv = 1) gives the same place as asking for the keys.
 struct CimaPaged {
   const int* table;
   int width;        // entries per slot in the table
@@ -86,12 +88,15 @@ struct CimaPaged {
   int page_size;
   int kv_heads;
   int head_dim;
+  int planes = 2;
   __device__ __forceinline__ size_t offset(int slot, int pos, int kv, int head) const {
     int e = pos / page_size;
     if (ring) e %= ring;
     const int page = table[(size_t)slot * width + e];
-    return ((((size_t)page * 2 + kv) * kv_heads + head) * page_size + (pos % page_size)) * (size_t)head_dim;
+    return ((((size_t)page * planes + (kv < planes ? kv : planes - 1)) * kv_heads + head) * page_size + (pos % page_size)) * (size_t)head_dim;
   }
+  // elements from a page's keys of one head to its values of the same head
+  __device__ __forceinline__ size_t value_offset() const { return planes == 2 ? (size_t)kv_heads * page_size * head_dim : 0; }
 };
 
 // One launch path for all kernels: programmatic stream serialisation (see above) and, for cluster_x > 1,

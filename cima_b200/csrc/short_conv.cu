@@ -1,0 +1,103 @@
+// A short causal convolution over time on each channel, added to its input:
+//   u[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - taps + 1 + j, c]        (zeros before a sequence's start)
+// for the ragged rows of a step.  What lies before the step's first row of a sequence comes from the
+// sequence's state [slots, taps - 1, C]: entry k holds the input of position len - (taps - 1) + k, len being the
+// positions the sequence held before the step (zeros where that is negative: a slot's state is zeroed when it
+// is opened).  Products and sums are float32 in ascending j, one rounding at the store, so a position's result
+// does not depend on whether its neighbours came with it or from the state.
+//
+// Two launches: the convolution (one thread per row and channel), then the state's update (one thread per
+// sequence and channel: the last taps - 1 inputs after the step).  When every sequence brings one row, a single
+// launch does both, each thread owning its (sequence, channel).
+#include "common.cuh"
+
+constexpr int CONV_MAX_TAPS = 16;
+constexpr int CONV_THREADS = 256;
+
+template <typename TA, bool ONE_ROW>
+__global__ void __launch_bounds__(CONV_THREADS)
+k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restrict__ state,
+             const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+             TA* __restrict__ u, int C, int taps) {
+  cima_pdl_wait();
+  const int row = blockIdx.x;
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c >= C) return;
+  const int seq = ONE_ROW ? row : row_seq[row];
+  const int k = ONE_ROW ? 0 : row - seq_first_row[seq];          // index of the row among the step's rows of its sequence
+  const int slot = seq_slot[seq];
+  TA* st = state + (size_t)slot * (taps - 1) * C + c;
+  const float* wc = w + (size_t)c * taps;
+  const float cur = cima_to_f32<TA>(h[(size_t)row * C + c]);
+  float acc = cur;
+  float old[CONV_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; j++) {
+    if (j >= taps) break;
+    const int back = taps - 1 - j;                                // positions back from this row
+    float v;
+    if (back == 0) v = cur;
+    else if (back <= k) v = cima_to_f32<TA>(h[(size_t)(row - back) * C + c]);
+    else v = cima_to_f32<TA>(st[(size_t)(taps - 1 - (back - k)) * C]);
+    old[j] = v;
+    acc = fmaf(wc[j], v, acc);
+  }
+  u[(size_t)row * C + c] = cima_from_f32<TA>(acc);
+  if (ONE_ROW) {
+    // the state moves on by one position: entries 1 .. taps - 2 go down, the row's input comes last
+    // (old[j] is the input `taps - 1 - j` positions back: old[1] ... old[taps - 1] are the new entries 0 ... taps - 2)
+#pragma unroll
+    for (int j = 1; j < CONV_MAX_TAPS; j++) {
+      if (j >= taps) break;
+      st[(size_t)(j - 1) * C] = cima_from_f32<TA>(old[j]);
+    }
+  }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(CONV_THREADS)
+k_short_conv_state(const TA* __restrict__ h, TA* __restrict__ state, const int* __restrict__ seq_slot,
+                   const int* __restrict__ seq_first_row, int C, int taps) {
+  cima_pdl_wait();
+  const int seq = blockIdx.x;
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c >= C) return;
+  const int first = seq_first_row[seq], n = seq_first_row[seq + 1] - first;
+  TA* st = state + (size_t)seq_slot[seq] * (taps - 1) * C + c;
+  TA v[CONV_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS - 1; k++) {
+    if (k >= taps - 1) break;
+    const int i = n - (taps - 1) + k;                             // the step's row that becomes entry k, if it is one
+    v[k] = i >= 0 ? h[(size_t)(first + i) * C + c] : st[(size_t)(k + n) * C];
+  }
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS - 1; k++) {
+    if (k >= taps - 1) break;
+    st[(size_t)k * C] = v[k];
+  }
+}
+
+// h, u [T, C] and state [slots, taps - 1, C] of one dtype; w [C, taps] float32.  one_row != 0: row r is sequence r's only row.
+extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* state, const int* row_seq, const int* seq_slot,
+                               const int* seq_first_row, void* u, int T, int n_seqs, int C, int taps, int one_row,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (taps < 1 || taps > CONV_MAX_TAPS) return cima_fail(CIMA_E_SIZE, "short_conv: %d taps are outside 1..%d", taps, CONV_MAX_TAPS);
+  if (C <= 0 || n_seqs <= 0) return cima_fail(CIMA_E_SIZE, "short_conv: %d channels and %d sequences must be positive", C, n_seqs);
+  if (one_row && T != n_seqs) return cima_fail(CIMA_E_ARG, "short_conv: %d rows are not one for each of %d sequences", T, n_seqs);
+  if (taps > 1 && !state) return cima_fail(CIMA_E_ARG, "short_conv: more than one tap needs the sequences' state");
+  const dim3 block(CONV_THREADS);
+  const unsigned cy = (unsigned)((C + CONV_THREADS - 1) / CONV_THREADS);
+#define RUN(TA) { \
+    int rc_; \
+    if (one_row) rc_ = cima_launch(k_short_conv<TA, true>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
+    else rc_ = cima_launch(k_short_conv<TA, false>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
+    if (rc_) return rc_; \
+    if (!one_row && taps > 1) { rc_ = cima_launch(k_short_conv_state<TA>, dim3(n_seqs, cy), block, (size_t)0, stream, 1, (const TA*)h, (TA*)state, seq_slot, seq_first_row, C, taps); if (rc_) return rc_; } }
+  if (dtype == CIMA_F32) RUN(float)
+  else if (dtype == CIMA_BF16) RUN(__nv_bfloat16)
+  else return cima_fail(CIMA_E_DTYPE, "short_conv: dtype code %d is neither float32 nor bfloat16", dtype);
+#undef RUN
+  return cima_launch_result();
+}

@@ -40,10 +40,11 @@ class Forecast:
 
 def forecast(plan: Dict[str, object], requests: Sequence[Sequence[object]], dtype: torch.dtype, max_tokens: int,
              hidden: int, vocab: int, widest: int, page_size: int = 64, shares: Sequence[int] = (),
-             extra_state: Sequence[StateRequest] = (), max_seqs: int = 0) -> Forecast:
+             extra_state: Sequence[StateRequest] = (), max_seqs: int = 0, streams: int = 1) -> Forecast:
     """``plan``: name -> TensorSpec (matrices are kept in ``dtype``, vectors in float32).  ``requests[i]``: what
     the mixer at site i asks of the cache.  ``widest``: the widest activation row of a layer (its gated
-    intermediate, twice, or its q/k/v row)."""
+    intermediate, twice, or its q/k/v row).  ``streams``: float32 copies of the residual stream that a step holds
+    (1, or with a depth average one per site and two more)."""
     elt = 4 if dtype is torch.float32 else 2
     weights = 0
     for spec in plan.values():
@@ -66,11 +67,11 @@ def forecast(plan: Dict[str, object], requests: Sequence[Sequence[object]], dtyp
         state += n_slots * _numel(r.shape) * torch.empty((), dtype=r.dtype).element_size()
     cache = state
     for r, sites in groups.items():
-        cache += sites * n_pages * 2 * r.n_kv_heads * page_size * r.head_dim * elt
+        cache += sites * n_pages * r.planes * r.n_kv_heads * page_size * r.head_dim * elt
     # a step of the longest prompt: the float32 residual, the widest activation and its input, logits of a batch;
     # and the recorded prompt steps that are kept, each with the activations of its rows
     from .graph import MAX_PROMPT_GRAPHS, recorded_prompt_rows
-    row = hidden * 4 + (widest + 2 * hidden) * elt
+    row = hidden * 4 * max(1, streams) + (widest + 2 * hidden) * elt
     rows = min(max_tokens, STEP_ROWS)
     scratch = rows * row + min(n_slots, 256) * vocab * 4 * 2
     scratch += MAX_PROMPT_GRAPHS * min(max_tokens, recorded_prompt_rows(weights, len(requests), elt)) * row

@@ -48,6 +48,15 @@ class Model:
                 raise ValueError(f"the schedule names layer {i}; the model has {len(spec.layers)}")
         self.blocks = [build_block(b, i, rt) for i, b in enumerate(spec.layers)]
         self.final_norm = build_norm(spec.final_norm, rt)
+        if spec.stream not in ("residual", "depth_average"):
+            raise ValueError(f"the model's stream '{spec.stream}' is neither 'residual' nor 'depth_average'")
+        self.depth = None                                   # what a layer reads: the stream itself, or a depth average
+        if spec.stream == "depth_average":
+            from ..parts.depth_average import DepthAverage
+            if len(spec.depth_names) != len(spec.schedule):
+                raise ValueError(f"a depth average needs one vector per site: {len(spec.depth_names)} names for "
+                                 f"{len(spec.schedule)} sites")
+            self.depth = DepthAverage(spec.depth_names, rt)
         self.config = None                                  # set by load_model
         self.step_rows = STEP_ROWS                          # a step of more rows runs in parts
         self.embedding: Optional[torch.Tensor] = None
@@ -60,6 +69,8 @@ class Model:
         p: Dict[str, TensorSpec] = {s.embed_name: TensorSpec((s.vocab, s.hidden))}
         for b in self.blocks:
             p.update(b.plan())
+        if self.depth is not None:
+            p.update(self.depth.plan())
         p.update(self.final_norm.plan(s.final_norm_name))
         if not s.tie_head:
             p[s.head_name] = TensorSpec((s.vocab, s.hidden))
@@ -83,6 +94,8 @@ class Model:
         del table
         for b in self.blocks:
             b.load(tensors)
+        if self.depth is not None:
+            self.depth.load(tensors)
         self.final_norm.load(tensors, s.final_norm_name)
         if not s.tie_head:
             self.head = Linear(tensors[s.head_name], None, self.rt)
@@ -94,6 +107,8 @@ class Model:
         out: Dict[str, torch.Tensor] = {s.embed_name: self.embedding}
         for b in self.blocks:
             out.update(b.state())
+        if self.depth is not None:
+            out.update(self.depth.state())
         out.update(self.final_norm.state(s.final_norm_name))
         if not s.tie_head:
             out[s.head_name] = self.head.weight
@@ -110,12 +125,14 @@ class Model:
     @property
     def graph_safe(self) -> bool:
         """Whether a decode step may be recorded as a CUDA graph: every layer's parts and the final norm say so."""
-        return all(getattr(b, "graph_safe", False) for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)
+        return (all(getattr(b, "graph_safe", False) for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)
+                and (self.depth is None or self.depth.graph_safe))
 
     def weight_bytes(self) -> int:
         """Bytes a decode step reads of the weights: every block, final norm and head once
         (embedding rows excluded unless the head shares the table)."""
-        return sum(b.nbytes() for b in self.blocks) + self.final_norm.nbytes() + self.head.nbytes()
+        return (sum(b.nbytes() for b in self.blocks) + self.final_norm.nbytes() + self.head.nbytes()
+                + (self.depth.nbytes() if self.depth is not None else 0))
 
     # ------------------------------------------------------------------ cache
     def make_cache(self, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = 64,
@@ -140,7 +157,7 @@ class Model:
         widest = max([int(getattr(b, "scratch_row", lambda: 0)()) for b in self.blocks] + [self.spec.hidden])
         return forecast(self.plan(), [self.blocks[layer].cache_requests(site) for site, layer in enumerate(sched)],
                         self.rt.dtype, max_tokens, self.spec.hidden, self.spec.vocab, widest, page_size, shares,
-                        extra_state, max_seqs or 0)
+                        extra_state, max_seqs or 0, streams=len(sched) + 2 if self.depth is not None else 1)
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -243,6 +260,8 @@ class Model:
 
     def forward(self, batch: StepBatch) -> torch.Tensor:
         K_, s = self.rt.kernels, self.spec
+        if self.depth is not None:
+            return self._forward_depth_average(batch)
         x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)
         # What a kernel leaves behind about the rows it wrote travels along as a RowsInfo, so that norms are
         # folded into the products around them (few rows) or run together with the residual add (many rows).
@@ -267,6 +286,23 @@ class Model:
             else:
                 nxt = self.final_norm if batch.want_all_in_order else None
             info = block.forward(x, batch, self.cache, site, info, nxt)
+        return self.project(x, batch, info)
+
+    def _forward_depth_average(self, batch: StepBatch) -> torch.Tensor:
+        """The same loop where a layer reads a depth average: the step keeps every stream (``DepthAverage``), site s
+        adds into plane s + 1, and the average that follows it, with the next norm, is one kernel."""
+        K_, s = self.rt.kernels, self.spec
+        order = [self.blocks[layer] for layer in s.schedule]
+        stack = self.depth.begin(batch.n_rows, s.hidden)
+        K_.embed(batch.tokens, self.embedding, stack[0], s.embed_scale)
+        x, info = self.depth.start(stack), None
+        for site, block in enumerate(order):
+            block.forward(x, batch, self.cache, site, info, None)
+            if site + 1 < len(order):
+                nxt = getattr(order[site + 1], "mixer_norm", None)
+            else:
+                nxt = self.final_norm if batch.want_all_in_order else None
+            x, info = self.depth.after(stack, site, nxt)
         return self.project(x, batch, info)
 
     def project(self, x: torch.Tensor, batch: StepBatch, info=None) -> torch.Tensor:

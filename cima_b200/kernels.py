@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 20
+ABI_VERSION = 21
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -67,12 +67,16 @@ _SIGNATURES = {
                              _i, _i, _i, _i, _vp],
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                             _f, _i, _i, _vp],
-    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
+                             _f, _i, _i, _i, _vp],
+    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
-    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                 _f, _i, _vp, _vp],
+                                 _f, _i, _vp, _i, _vp],
+    "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
+    "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
@@ -414,14 +418,15 @@ class Kernels:
             args = (kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size)
         else:
             args = (None, None, 0, 0, 1)
-        if not self._admit("attention_plain", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
+        planes = int(getattr(kv, "planes", 2)) if from_cache else 2
+        if not self._admit("attention_plain", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim, planes)): return
         self._check(self.lib.cima_attention_plain(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], *args,
                                                   row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                                                   seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                   n_heads, n_kv_heads, head_dim, scale, window,
-                                                  1 if from_cache else 0, self._stream()), "attention_plain")
+                                                  1 if from_cache else 0, planes, self._stream()), "attention_plain")
 
-    def _attention_work(self, qkv, n_heads, n_kv_heads, head_dim):
+    def _attention_work(self, qkv, n_heads, n_kv_heads, head_dim, planes: int = 2):
         """(bytes, operations) of an attention launch while a step is profiled: the keys and values of the step's
         sequences (``profile.kv_tokens``: positions that the step's rows read, each once) and the products over the
         (query, key) pairs (``profile.qk_pairs``); the step's maker states both."""
@@ -429,7 +434,7 @@ class Kernels:
         if p is None:
             return 0, 0
         elt = qkv.element_size()
-        return (2.0 * p.kv_tokens * n_kv_heads * head_dim * elt + 2.0 * qkv.shape[0] * n_heads * head_dim * elt,
+        return (float(planes) * p.kv_tokens * n_kv_heads * head_dim * elt + 2.0 * qkv.shape[0] * n_heads * head_dim * elt,
                 4.0 * p.qk_pairs * n_heads * head_dim)
 
     def library_mm(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
@@ -500,12 +505,12 @@ class Kernels:
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim) or batch.q_tile_seq.numel() != batch.q_tile_row0.numel():
             raise KernelError(f"attention_extend: out {tuple(out.shape)} or the block list do not fit")
-        if not self._admit("attention_extend", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
+        if not self._admit("attention_extend", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim, kv.planes)): return
         self._check(self.lib.cima_attention_extend(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_seq.data_ptr(), batch.q_tile_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(), out.data_ptr(), out.shape[1],
-            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, self._stream()), "attention_extend")
+            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, kv.planes, self._stream()), "attention_extend")
 
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                              head_dim: int, scale: float, window: int, kv=None) -> None:
@@ -520,7 +525,7 @@ class Kernels:
             raise KernelError(f"attention_prefill_tc: out {tuple(out.shape)} or the block list do not fit")
         if self._error_flag is None:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=qkv.device)
-        if not self._admit("attention_prefill_tc", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
+        if not self._admit("attention_prefill_tc", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim, kv.planes if kv is not None else 2)): return
         if kv is not None:
             self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
             self._check(self.lib.cima_attention_extend_tc(
@@ -528,7 +533,7 @@ class Kernels:
                 batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.storage.shape[0], kv.block_table.data_ptr(),
                 kv.block_table.shape[1], kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(),
                 out.data_ptr(), out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
-                self._error_flag.data_ptr(), self._stream()), "attention_extend_tc")
+                self._error_flag.data_ptr(), kv.planes, self._stream()), "attention_extend_tc")
             return
         self._check(self.lib.cima_attention_prefill_tc(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_tc_seq.data_ptr(), batch.q_tile_tc_row0.data_ptr(),
@@ -568,7 +573,7 @@ class Kernels:
                 # a short context is a few pages: one block reads them in less time than the merge of splits takes
                 if max_len <= short_context(head_dim):
                     n_splits = 1
-        if not self._admit(f"attention_decode[{n_splits} splits]", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
+        if not self._admit(f"attention_decode[{n_splits} splits]", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim, kv.planes)): return
         part_o = part_ml = None
         if n_splits > 1:
             part_o = self._scratch("attn_o", B * n_heads * n_splits * head_dim, qkv.device)
@@ -577,7 +582,7 @@ class Kernels:
             qkv.data_ptr(), qkv.shape[1], kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, seq_slot.data_ptr(), seq_len.data_ptr(), _ptr(part_o), _ptr(part_ml),
             out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, int(early),
-            self._stream()), "attention_decode")
+            kv.planes, self._stream()), "attention_decode")
         if n_splits > 1:
             self.launches += 1
 
@@ -591,6 +596,72 @@ class Kernels:
                 self._retired.append(t)
             t = self._scratch_bufs[name] = torch.empty(numel, dtype=torch.float32, device=device)
         return t
+
+    # ------------------------------------------------------------------ short convolution, depth average, latents
+    def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], batch, out: torch.Tensor) -> None:
+        """out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j] per channel, causal within each sequence of the
+        step; what lies before the step's rows comes from ``state`` [slots, taps - 1, C] (the sequences' last
+        inputs), which is brought up to date.  ``w`` [C, taps] float32; h, out, state of one dtype."""
+        self._need(h, "h", None, 2); self._need(w, "w", torch.float32, 2); self._need(out, "out", h.dtype, 2)
+        T, C = h.shape
+        taps = w.shape[1]
+        if w.shape[0] != C or out.shape != h.shape:
+            raise KernelError(f"short_conv: h {tuple(h.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+        if taps > 1:
+            self._need(state, "state", h.dtype, 3)
+            if tuple(state.shape[1:]) != (taps - 1, C):
+                raise KernelError(f"short_conv: state is {tuple(state.shape)}, expected [slots, {taps - 1}, {C}]")
+        one_row = batch.n_rows == batch.n_seqs
+        if not self._admit("short_conv", 2 * T * C * h.element_size()): return
+        self._check(self.lib.cima_short_conv(h.data_ptr(), dtype_code(h.dtype), w.data_ptr(), _ptr(state if taps > 1 else None),
+                                             batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_first_row.data_ptr(),
+                                             out.data_ptr(), T, batch.n_seqs, C, taps, int(one_row), self._stream()), "short_conv")
+        if not one_row and taps > 1:
+            self.launches += 1
+
+    def depth_average(self, stack: torch.Tensor, n: int, a: torch.Tensor, x: torch.Tensor,
+                      w: Optional[torch.Tensor] = None, eps: float = 0.0, y: Optional[torch.Tensor] = None) -> None:
+        """x = sum_{j < n} a[j] * stack[j] (float32 [planes, T, H]); with ``w`` also y = RMSNorm(x; w, eps).
+        ``x`` may be a plane of ``stack`` beyond the first n."""
+        self._need(stack, "stack", torch.float32, 3); self._need(a, "a", torch.float32, 1); self._need(x, "x", torch.float32, 2)
+        P, T, H = stack.shape
+        if not (1 <= n <= P) or a.numel() != n or tuple(x.shape) != (T, H):
+            raise KernelError(f"depth_average: stack {tuple(stack.shape)}, {n} streams, a {tuple(a.shape)}, x {tuple(x.shape)} do not agree")
+        if (w is None) != (y is None):
+            raise KernelError("depth_average: the norm's weight and its output go together")
+        if w is not None:
+            self._need(w, "w", torch.float32, 1); self._need(y, "y", None, 2)
+            if w.numel() != H or tuple(y.shape) != (T, H):
+                raise KernelError(f"depth_average: w {tuple(w.shape)} / y {tuple(y.shape)} do not fit {(T, H)}")
+        if not self._admit("depth_average", T * H * (4 * (n + 1) + (y.element_size() if y is not None else 0))): return
+        self._check(self.lib.cima_depth_average(stack.data_ptr(), T * H, a.data_ptr(), n, x.data_ptr(), _ptr(w), _ptr(y),
+                                                dtype_code(y.dtype) if y is not None else F32, T, H, eps, self._stream()),
+                    "depth_average")
+
+    def latent_append(self, raw: torch.Tensor, g: torch.Tensor, eps: float, kv, batch) -> None:
+        """c = RMSNorm(raw; g, eps) per row, written to the row's position in the layer's pages (one plane, one
+        head of raw.shape[1] values).  ``raw`` [T, R] may be a column slice of a wider matrix."""
+        self._need(g, "g", torch.float32, 1); self._need(kv.storage, "cache", raw.dtype, 5)
+        T, R = raw.shape
+        if raw.stride(1) != 1 or g.numel() != R or tuple(kv.storage.shape[1:]) != (1, 1, kv.page_size, R):
+            raise KernelError(f"latent_append: raw {tuple(raw.shape)}, g {tuple(g.shape)}, pages {tuple(kv.storage.shape)} do not agree")
+        if not self._admit("latent_append", 2 * T * R * raw.element_size()): return
+        self._check(self.lib.cima_latent_append(raw.data_ptr(), dtype_code(raw.dtype), raw.stride(0), g.data_ptr(), eps,
+                                                kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
+                                                kv.ring_pages, kv.page_size, batch.row_pos.data_ptr(), batch.row_seq.data_ptr(),
+                                                batch.seq_slot.data_ptr(), T, R, self._stream()), "latent_append")
+
+    def head_linear(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t, h, :] = a[t, h, :] @ w[h].T for every head: a [T, heads * K] (rows may be slices of a wider
+        matrix), w [heads, N, K], out [T, heads * N]; one dtype."""
+        self._need(w, "w", a.dtype, 3); self._need(out, "out", a.dtype, 2)
+        heads, N, K = w.shape
+        T = a.shape[0]
+        if a.dim() != 2 or a.stride(1) != 1 or a.shape[1] != heads * K or tuple(out.shape) != (T, heads * N):
+            raise KernelError(f"head_linear: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+        if not self._admit("head_linear", (w.numel() + a.numel() + out.numel()) * a.element_size(), 2.0 * T * heads * N * K): return
+        self._check(self.lib.cima_head_linear(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K,
+                                              a.stride(0), out.stride(0), self._stream()), "head_linear")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:

@@ -1,5 +1,6 @@
 """Arrangement of a layer's parts.  ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x))
-(src/models/transformer.rs:1024-1319).  The block builds its parts from the spec through the
+(src/models/transformer.rs:1024-1319).  ``parallel``: h = norm(x); x += mixer(conv(h)) + feed_forward(h): one norm
+feeds both sublayers, the mixer optionally through a short causal convolution, the feed-forward optionally absent.  The block builds its parts from the spec through the
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
@@ -96,4 +97,77 @@ class PreNormBlock:
         return None
 
 
+class ParallelBlock:
+    """h = norm(x); x += mixer(u) + feed_forward(h), with u = h, or h + conv(h) where the spec has a ``mixer_conv``
+    (a ``ShortConv``, which keeps a sequence's newest inputs as state).  Both sublayers add into the float32
+    stream, so their sum is formed there."""
+
+    def __init__(self, spec, layer: int, rt):
+        from .short_conv import ShortConv
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.mixer_norm = build_norm(spec.mixer_norm, rt)
+        self.mixer = build_mixer(spec.mixer, layer, rt)
+        self.conv = ShortConv(spec.mixer_conv, rt) if spec.mixer_conv is not None else None
+        self.feed_forward = build_feed_forward(spec.feed_forward, layer, rt) if spec.feed_forward is not None else None
+
+    def _named(self):
+        """(part, the arguments of its plan / load / state) for every part that owns tensors."""
+        s = self.spec
+        sfx = s.names.get("suffix", ".weight")
+        out = [(self.mixer_norm, (f"{s.prefix}{s.names['mixer_norm']}{sfx}",)), (self.mixer, (s.prefix, s.names))]
+        if self.conv is not None:
+            out.append((self.conv, (f"{s.prefix}{s.names['mixer_conv']}{sfx}",)))
+        if self.feed_forward is not None:
+            out.append((self.feed_forward, (s.prefix, s.names)))
+        return out
+
+    def plan(self) -> Dict[str, TensorSpec]:
+        p: Dict[str, TensorSpec] = {}
+        for part, args in self._named():
+            p.update(part.plan(*args))
+        return p
+
+    def load(self, tensors) -> None:
+        for part, args in self._named():
+            part.load(tensors, *args)
+
+    def state(self) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        for part, args in self._named():
+            if not hasattr(part, "state"):
+                raise NotImplementedError(f"{type(part).__name__} of layer {self.layer} offers no state(): its tensors "
+                                          f"cannot be given back by name")
+            out.update(part.state(*args))
+        return out
+
+    def cache_requests(self, site: int) -> List[object]:
+        reqs = list(self.mixer.cache_requests(site))
+        if self.conv is not None:
+            reqs += self.conv.cache_requests(site)
+        return reqs
+
+    def scratch_row(self) -> int:
+        parts = [p for p in (self.mixer, self.feed_forward) if p is not None]
+        return max(int(getattr(p, "scratch_row", lambda: 0)()) for p in parts)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p, _ in self._named())
+
+    def nbytes(self) -> int:
+        return sum(p.nbytes() for p, _ in self._named())
+
+    def forward(self, x: torch.Tensor, batch, cache, site: int, info=None, next_norm=None):
+        if info is not None and getattr(info, "norm", None) is self.mixer_norm and info.h is not None:
+            h = info.h                                             # the rows came normalised already
+        else:
+            h = self.mixer_norm(x)
+        u = self.conv.forward(h, batch, cache, site) if self.conv is not None else h
+        self.mixer.forward(u, x, batch, cache, site)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(h, x, batch)
+        return None
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel", ParallelBlock)

@@ -27,24 +27,29 @@ class GatedMLP:
         self.gate_up = None
         self.down = None
 
+    @staticmethod
+    def _names(prefix: str, names: Dict[str, str]):
+        sfx = names.get("suffix", ".weight")
+        return tuple(f"{prefix}{names[k]}{sfx}" for k in ("gate", "up", "down"))
+
     def plan(self, prefix: str, names: Dict[str, str]) -> Dict[str, TensorSpec]:
         s = self.spec
-        return {f"{prefix}{names['gate']}.weight": TensorSpec((s.intermediate, s.hidden)),
-                f"{prefix}{names['up']}.weight": TensorSpec((s.intermediate, s.hidden)),
-                f"{prefix}{names['down']}.weight": TensorSpec((s.hidden, s.intermediate))}
+        gate, up, down = self._names(prefix, names)
+        return {gate: TensorSpec((s.intermediate, s.hidden)), up: TensorSpec((s.intermediate, s.hidden)),
+                down: TensorSpec((s.hidden, s.intermediate))}
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
-        self.gate_up = GatedLinearPair(tensors[f"{prefix}{names['gate']}.weight"],
-                                       tensors[f"{prefix}{names['up']}.weight"], self.rt, self.spec.activation)
-        self.down = Linear(tensors[f"{prefix}{names['down']}.weight"], None, self.rt)
+        gate, up, down = self._names(prefix, names)
+        self.gate_up = GatedLinearPair(tensors[gate], tensors[up], self.rt, self.spec.activation)
+        self.down = Linear(tensors[down], None, self.rt)
 
     def nbytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
 
     def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
         w, I = self.gate_up.lin.weight, self.spec.intermediate
-        return {f"{prefix}{names['gate']}.weight": w[:I], f"{prefix}{names['up']}.weight": w[I:],
-                f"{prefix}{names['down']}.weight": self.down.weight}
+        gate, up, down = self._names(prefix, names)
+        return {gate: w[:I], up: w[I:], down: self.down.weight}
 
     def scratch_row(self) -> int:
         return 2 * self.spec.intermediate

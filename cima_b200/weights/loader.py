@@ -28,7 +28,7 @@ from .safetensors_io import open_model_files
 @dataclass(frozen=True)
 class TensorSpec:
     shape: Tuple[int, ...]
-    init: str = "normal"        # random-weights mode: "normal" N(0, std) | "ones_normal" 1 + N(0, std)
+    init: str = "normal"        # random-weights mode: "normal" N(0, std) | "ones_normal" 1 + N(0, std) | "mean" (1 + N(0, std)) / count
     std: float = 0.02
 
 

@@ -1,8 +1,9 @@
 """Random-weights mode: a model folder (config.json, model.safetensors) from a configuration and a seed.
 
 Every tensor of the model's plan is drawn from its own generator, seeded by
-(seed, tensor name), so a tensor's values depend on nothing else: N(0, 0.02) for
-matrices and biases, 1 + N(0, 0.02) for norm weights, stored as bfloat16.  The
+(seed, tensor name), so a tensor's values depend on nothing else: N(0, std) for
+matrices and biases, 1 + N(0, std) for norm weights, (1 + N(0, std)) / count for the weights of an average, stored
+as bfloat16 (std 0.02 unless the part's plan names another).  The
 reference's stand-in for a checkpoint is ``MockWeights`` (src/selftest.rs:38-83,
 :123-158): xorshift values under the real tensor names, in memory only.
 """
@@ -31,7 +32,7 @@ def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, 
     """The tensor ``name`` drawn from the generator seeded by (seed, name), in slabs of ``_SLAB`` values in float32
     that are rounded into ``dtype`` as they come.  On the CPU a slab (a multiple of 16 values) continues the
     generator's sequence exactly where the last one ended, so the values do not depend on the slab size."""
-    if spec.init not in ("normal", "ones_normal"):
+    if spec.init not in ("normal", "ones_normal", "mean"):
         raise ValueError(f"unknown init '{spec.init}' for tensor '{name}'")
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
@@ -42,8 +43,10 @@ def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, 
     for lo in range(0, n, _SLAB):
         part = scratch[:min(_SLAB, n - lo)]
         part.normal_(0.0, spec.std, generator=g)
-        if spec.init == "ones_normal":
+        if spec.init in ("ones_normal", "mean"):
             part += 1.0
+        if spec.init == "mean":                      # weights of an average: (1 + N(0, std)) / count
+            part /= float(n)
         flat[lo:lo + part.numel()].copy_(part)
     return out
 

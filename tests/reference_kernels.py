@@ -159,7 +159,9 @@ class ReferenceKernels:
                         head_dim, scale, window, from_cache):
         T = qkv.shape[0]
         rep = n_heads // n_kv_heads
-        heads = qkv[:, :(n_heads + 2 * n_kv_heads) * head_dim].view(T, n_heads + 2 * n_kv_heads, head_dim)
+        vplane = int(getattr(kv, "planes", 2)) - 1 if from_cache else 1      # one plane: the values are the keys
+        cols = (n_heads + (0 if from_cache else 2 * n_kv_heads)) * head_dim
+        heads = qkv[:, :cols].view(T, cols // head_dim, head_dim)
         for r in range(T):
             pos, seq = int(row_pos[r]), int(row_seq[r])
             lo = max(0, pos + 1 - window) if window > 0 else 0
@@ -169,7 +171,7 @@ class ReferenceKernels:
                 for j in range(lo, pos + 1):
                     page, off = _page_offset(kv, slot, j)
                     ks.append(kv.storage[page, 0, :, off, :])
-                    vs.append(kv.storage[page, 1, :, off, :])
+                    vs.append(kv.storage[page, vplane, :, off, :])
                 k = torch.stack(ks).to(self.compute)       # [keys, nkv, hd]
                 v = torch.stack(vs).to(self.compute)
             else:
@@ -209,3 +211,51 @@ class ReferenceKernels:
             tokens[i] = tok
             ring[slot, pushed % 64] = tok
             count[slot] = pushed + 1
+
+
+# ---------------------------------------------------------------------- short convolution, depth average, latents
+def _short_conv(self, h, w, state, batch, out):
+    taps = w.shape[1]
+    first = batch.seq_first_row
+    hc = h.to(self.compute)
+    for s in range(batch.n_seqs):
+        lo, hi = int(first[s]), int(first[s + 1])
+        slot = int(batch.seq_slot[s])
+        past = state[slot].to(self.compute) if taps > 1 else hc[:0]
+        line = torch.cat([past, hc[lo:hi]])                      # the inputs from taps - 1 positions before the step on
+        n = hi - lo
+        acc = hc[lo:hi].clone()
+        for j in range(taps):
+            acc = acc + w[:, j].to(self.compute) * line[j:j + n]
+        out[lo:hi] = acc.to(out.dtype)
+        if taps > 1:
+            state[slot] = line[n:].to(state.dtype)
+
+
+def _depth_average(self, stack, n, a, x, w=None, eps=0.0, y=None):
+    acc = torch.zeros_like(x)
+    for j in range(n):
+        acc = acc + a[j] * stack[j]
+    x.copy_(acc)
+    if w is not None:
+        self.rmsnorm(x, w, eps, y)
+
+
+def _latent_append(self, raw, g, eps, kv, batch):
+    r = raw.to(self.compute)
+    c = r / torch.sqrt((r * r).mean(dim=-1, keepdim=True) + eps) * g.to(self.compute)
+    for t in range(raw.shape[0]):
+        page, off = _page_offset(kv, int(batch.seq_slot[int(batch.row_seq[t])]), int(batch.row_pos[t]))
+        kv.storage[page, 0, 0, off, :] = c[t].to(kv.storage.dtype)
+
+
+def _head_linear(self, a, w, out):
+    heads, N, K = w.shape
+    y = torch.einsum("thk,hnk->thn", a.reshape(a.shape[0], heads, K).to(self.compute), w.to(self.compute))
+    out.copy_(y.reshape(a.shape[0], heads * N).to(out.dtype))
+
+
+ReferenceKernels.short_conv = _short_conv
+ReferenceKernels.depth_average = _depth_average
+ReferenceKernels.latent_append = _latent_append
+ReferenceKernels.head_linear = _head_linear
