@@ -62,12 +62,28 @@ def plain_latent_attention(u: torch.Tensor, c: torch.Tensor, w_q, w_uk, w_uv, w_
     k = (c @ w_uk.T).view(T, heads, dim)
     v = (c @ w_uv.T).view(T, heads, vdim)
     att = torch.zeros(T, heads, vdim, dtype=u.dtype)
-    for t in range(T):
-        for hd in range(heads):
-            s = (k[: t + 1, hd] @ q[t, hd]) * scale
-            p = torch.softmax(s, dim=0)
-            att[t, hd] = p @ v[: t + 1, hd]
+    hidden = torch.triu(torch.ones(T, T, dtype=torch.bool), diagonal=1)        # [query, key]: key after query
+    for hd in range(heads):
+        s = (q[:, hd] @ k[:, hd].T) * scale
+        p = torch.softmax(s.masked_fill(hidden, float("-inf")), dim=1)
+        att[:, hd] = p @ v[:, hd]
     return att.reshape(T, heads * vdim) @ w_o.T
+
+
+def plain_latent_attention_one(u_t: torch.Tensor, c_past: torch.Tensor, w_q, w_uk, w_uv, w_o, heads: int, dim: int,
+                               vdim: int, scale: float) -> torch.Tensor:
+    """One position on its own, key by key: u_t [W] its input, c_past [n, R] the latents of positions 0 .. t."""
+    q = (w_q @ u_t).view(heads, dim)
+    out = torch.zeros(heads, vdim, dtype=u_t.dtype)
+    for hd in range(heads):
+        ks = [w_uk[hd * dim:(hd + 1) * dim] @ c for c in c_past]
+        vs = [w_uv[hd * vdim:(hd + 1) * vdim] @ c for c in c_past]
+        s = torch.stack([(kk * q[hd]).sum() * scale for kk in ks])
+        p = torch.exp(s - s.max())
+        p = p / p.sum()
+        for pj, vj in zip(p, vs):
+            out[hd] += pj * vj
+    return w_o @ out.reshape(heads * vdim)
 
 
 def plain_gated(h: torch.Tensor, w_gate, w_up, w_down) -> torch.Tensor:
