@@ -95,6 +95,126 @@ def reference_arm():
     return 0
 
 
+def design_bench(a) -> int:
+    """Decode (batch 1 and --batch, context --prompt) and prefill (2,048 tokens) of a design's shapes beside the Qwen2
+    shape of equal width, heads, feed-forward and vocabulary; --layers layers of each (default 4: the per-layer
+    figures do not depend on the count, and both models carry the same head).  With --per-kernel: every launch of
+    one decode step and one prompt step of the design's first size.  One JSON line."""
+    import numpy as np
+    import torch
+    import cima_b200
+    from cima_b200.config.shapes import SHAPES, TWINS
+    from cima_b200.engine import StepEntry
+    from cima_b200.sampling import GenOptions
+
+    pk = peaks()
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    n_layers = a.layers or 4
+    steps, warmup = min(a.steps, 128), a.warmup
+    rng = np.random.default_rng(0)
+
+    def cut(raw):
+        raw = json.loads(json.dumps(raw))
+        if "layers" in raw:
+            raw["layers"] = raw["layers"][:n_layers]
+        else:
+            raw["num_hidden_layers"] = n_layers
+        return raw
+
+    def load(raw, batch):
+        per_seq = a.prompt + steps + warmup + 64
+        return cima_b200.load(config=raw, seed=0, draw="device", dtype="bfloat16", device=dev, max_seqs=batch,
+                              max_tokens=max(batch * (-(-per_seq // 64) * 64), 2048 + 64), max_batch=batch,
+                              pipeline=False, verbose=False)
+
+    def timed(fn, reps=1):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3
+
+    def measure(raw):
+        lm = load(raw, a.batch)
+        model, st, K = lm.model, lm.stepper, lm.model.rt.kernels
+        V = model.spec.vocab
+        greedy = GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=steps, ignore_eos=True)
+        out = {"weight_bytes": model.weight_bytes(), "recorded": bool(st.use_graphs)}
+        kv_bytes = sum(g.storage.element_size() * len(g.layers) * g.request.planes * g.request.n_kv_heads * g.request.head_dim
+                       for g in model.cache.groups)
+        for batch in sorted({1, a.batch}):
+            prompts = [rng.integers(0, V, size=a.prompt).tolist() for _ in range(batch)]
+            slots = st.open(batch)
+            try:
+                opts = [greedy] * batch
+                first = st.prefill(slots, prompts, opts)
+                last = st.decode(slots, first, opts)
+                st.decode_on_device(slots, last, opts, warmup, reach=warmup + steps)
+                secs = timed(lambda: st.decode_on_device(slots, None, opts, steps))
+                lps = st.recorded_launches(batch)
+            finally:
+                st.close(slots)
+            ctx = a.prompt + 1 + warmup + steps / 2.0
+            gbs = (out["weight_bytes"] + batch * ctx * kv_bytes) / (secs / steps) / 1e9
+            out[f"decode_b{batch}"] = {"tokens_per_s": batch * steps / secs, "ms_per_step": secs / steps * 1e3,
+                                       "launches_per_step": lps, "hbm_frac": gbs / pk["hbm_gbs"]}
+        T = 2048
+        prompt = rng.integers(0, V, size=T).tolist()
+        tok = torch.empty(1, dtype=torch.int32, device=dev)
+
+        def prefill_once():
+            (slot,) = model.cache.open(1)
+            try:
+                K.argmax(model.step([StepEntry(slot, prompt, [T - 1])]), tok)
+            finally:
+                model.cache.close([slot])
+        for _ in range(3):
+            prefill_once()
+        psecs = timed(prefill_once, 3) / 3
+        out["prefill_2048"] = {"tokens_per_s": T / psecs, "ms": psecs * 1e3}
+        model.check_device()
+        del lm, model, st
+        torch.cuda.empty_cache()
+        return out
+
+    sizes = [s.strip() for s in a.sizes.split(",") if s.strip()]
+    if a.per_kernel:
+        from cima_b200.engine.profile import profile_decode, profile_prompt, table
+        for name in (f"{a.design}-{sizes[0]}", TWINS[f"{a.design}-{sizes[0]}"]):
+            lm = load(cut(SHAPES[name]), a.batch)
+            st = lm.stepper
+            greedy = GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=steps, ignore_eos=True)
+            prompts = [rng.integers(0, lm.model.spec.vocab, size=a.prompt).tolist() for _ in range(a.batch)]
+            slots = st.open(a.batch)
+            try:
+                opts = [greedy] * a.batch
+                rows = profile_decode(st, slots, st.prefill(slots, prompts, opts), opts)
+            finally:
+                st.close(slots)
+            print(f"{name}, {n_layers} layers: decode step, batch {a.batch}, context {a.prompt} (peaks {pk['source']}):")
+            print(table(rows, pk["hbm_gbs"], pk["bf16_tflops"], tokens=a.batch))
+            print(f"\n{name}: prompt step, one prompt of {a.prompt} tokens:")
+            print(table(profile_prompt(lm.model, [a.prompt]), pk["hbm_gbs"], pk["bf16_tflops"]))
+            print()
+            del lm, st
+            torch.cuda.empty_cache()
+        return 0
+    results = {}
+    with ClockSampler() as clocks:
+        for s in sizes:
+            name = f"{a.design}-{s}"
+            results[name] = measure(cut(SHAPES[name]))
+            results[TWINS[name]] = measure(cut(SHAPES[TWINS[name]]))
+    print(json.dumps({"design": a.design, "layers": n_layers, "batch": a.batch, "context": a.prompt, "steps": steps,
+                      "warmup": warmup, "dtype": "bf16", "data": "synthetic: random weights seed 0, uniform random token ids",
+                      "peaks": pk, "clocks": clocks.summary(), "results": results}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -108,6 +228,9 @@ def main(argv=None) -> int:
                     "defined on the default, Qwen2.5-7B)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--design", default=None, choices=["vunovik"], help="instead of the metric line: decode and prefill "
+                    "throughput of that design's shapes beside the Qwen2 shape of equal size (--sizes, --layers)")
+    ap.add_argument("--sizes", default="1.5b,3b,7b", help="with --design: the shapes to measure (0.5b, 1.5b, 3b, 7b)")
     ap.add_argument("--per-kernel", action="store_true", help="instead of the metric line: every launch of one decode step "
                     "(--batch) and of one prompt step (--prompt tokens) with its time inside the step, bytes and flops "
                     "over time against the measured peaks; use few layers (--layers 2)")
@@ -118,6 +241,8 @@ def main(argv=None) -> int:
         print(f"bench.py measures one GPU only (this library does no multi-GPU work); --gpus {a.gpus} is not run")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.design:
+        return design_bench(a)
 
     import numpy as np
     import torch

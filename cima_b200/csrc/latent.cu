@@ -10,9 +10,9 @@
 // which moves a query into the latents' space (w = the key projection's head, transposed) and an attention
 // result out of it (w = the value projection's head).  FFMA with one float32 accumulator per output in ascending
 // k: the same bits for a row whatever comes with it.  It serves the 32-bit path at every size and the
-// bfloat16 path for the few rows of a decode step; many bfloat16 rows go to the tensor-core variant below.
+// bfloat16 path for the few rows of a decode step; many bfloat16 rows are the caller's to give to the library's
+// batched product, as it does with the other products of many rows.
 #include "common.cuh"
-#include <mma.h>
 
 // ------------------------------------------------------------------------------------------- latent_append
 template <typename TA>
@@ -108,96 +108,84 @@ k_head_linear(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict
   }
 }
 
-// Few rows (a decode step): one warp per (head, output n) would leave the weights' rows to single warps; instead a
-// block takes one head and 32 outputs, each warp 4 of them, the lanes stride over k (coalesced reads of the weight
-// rows), and the rows of A sit in shared memory.  The sum over k is a lane's partial sum in ascending k, then the
-// lanes' sums in a fixed order: the same bits for a row whatever the batch.
+// Few rows (a decode step): a block takes 32 outputs n of one head; warp m of the block computes them for row m
+// of A, lane l the output n0 + l: the lane walks its row of the head's matrix once (16-byte loads, a chunk of 64 k in
+// registers at a time) against the row of A in shared memory (every lane reads the same value: a broadcast), one
+// float32 accumulator in ascending k.  All warps of a block read the same weight rows, which the first one brings
+// into the first-level cache.  The work is a few hundred KB of weights; its time is latency, so the chain of a
+// thread is kept short (K fused multiply-adds) and the blocks many.
 constexpr int HL_FEW_ROWS = 8;
+constexpr int HL_FEW_K = 64;          // k of a row that a thread holds in registers at a time
+
+template <typename TA> struct HlVec;
+template <> struct HlVec<float> { static constexpr int N = 4; };
+template <> struct HlVec<__nv_bfloat16> { static constexpr int N = 8; };
 
 template <typename TA>
-__global__ void __launch_bounds__(256)
-k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict__ out, int M, int N, int K, int lda, int ldo) {
-  cima_pdl_wait();
-  extern __shared__ float a_sh[];                       // [M][K]
+__global__ void __launch_bounds__(32 * HL_FEW_ROWS)
+k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict__ out, int M, int N, int K, int lda, int ldo,
+                  int vec) {
+  extern __shared__ __align__(16) float a_sh[];         // [M][Kp], Kp = K rounded up to 4
+  const int Kp = (K + 3) & ~3;
   const int head = blockIdx.y;
-  A += (size_t)head * K;
-  W += (size_t)head * N * K;
-  out += (size_t)head * N;
-  for (int e = threadIdx.x; e < M * K; e += blockDim.x) a_sh[e] = cima_to_f32<TA>(A[(size_t)(e / K) * lda + (e % K)]);
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int q = 0; q < 4; q++) {
-    const int n = blockIdx.x * 32 + warp * 4 + q;
-    if (n >= N) break;
-    const TA* wr = W + (size_t)n * K;
-    float acc[HL_FEW_ROWS];
+  const int lane = threadIdx.x & 31, m = threadIdx.x >> 5;
+  const int n = blockIdx.x * 32 + lane;
+  const bool live = n < N;
+  const TA* wr = W + ((size_t)head * N + (live ? n : 0)) * K;
+  constexpr int V = HlVec<TA>::N;
+  float w[HL_FEW_K];
+  // the first chunk of the weights does not depend on the kernel before this one: it is requested before the wait
+  const int kn0 = min(HL_FEW_K, K);
+  if (vec && kn0 == HL_FEW_K) {
 #pragma unroll
-    for (int m = 0; m < HL_FEW_ROWS; m++) acc[m] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float w = cima_to_f32<TA>(wr[k]);
+    for (int q = 0; q < HL_FEW_K / V; q++) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(wr + q * V);
+      const TA* e = reinterpret_cast<const TA*>(&raw);
 #pragma unroll
-      for (int m = 0; m < HL_FEW_ROWS; m++)
-        if (m < M) acc[m] = fmaf(a_sh[m * K + k], w, acc[m]);
+      for (int i = 0; i < V; i++) w[q * V + i] = cima_to_f32<TA>(e[i]);
     }
+  } else {
 #pragma unroll
-    for (int m = 0; m < HL_FEW_ROWS; m++) {
-      if (m >= M) break;
-      float v = acc[m];
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) out[(size_t)m * ldo + n] = cima_from_f32<TA>(v);
-    }
+    for (int q = 0; q < HL_FEW_K; q++) w[q] = q < kn0 ? cima_to_f32<TA>(wr[q]) : 0.f;
   }
-}
-
-// Many bfloat16 rows: warp-level tensor-core tiles (16 x 16 x 16, float32 accumulators), a block of 8 warps on
-// 64 rows x 32 outputs of one head, operands staged through shared memory with zero fill at the edges.
-constexpr int HT_BM = 64, HT_BN = 32, HT_BK = 32;
-
-__global__ void __launch_bounds__(256)
-k_head_linear_mma(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out,
-                  int M, int N, int K, int lda, int ldo) {
-  using namespace nvcuda;
   cima_pdl_wait();
-  __shared__ __align__(32) __nv_bfloat16 As[HT_BM][HT_BK + 8];
-  __shared__ __align__(32) __nv_bfloat16 Ws[HT_BN][HT_BK + 8];
-  __shared__ __align__(32) float Cs[8][16][16 + 4];
-  const int head = blockIdx.z;
   A += (size_t)head * K;
-  W += (size_t)head * N * K;
-  out += (size_t)head * N;
-  const int m0 = blockIdx.y * HT_BM, n0 = blockIdx.x * HT_BN;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wm = warp >> 1, wn = warp & 1;              // 4 x 2 warps, one 16 x 16 tile each
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-  wmma::fill_fragment(c, 0.f);
-  const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
-  for (int k0 = 0; k0 < K; k0 += HT_BK) {
-    for (int e = threadIdx.x; e < HT_BM * HT_BK; e += 256) {
-      const int r = e / HT_BK, kk = e % HT_BK;
-      As[r][kk] = (m0 + r < M && k0 + kk < K) ? A[(size_t)(m0 + r) * lda + k0 + kk] : zero;
-    }
-    for (int e = threadIdx.x; e < HT_BN * HT_BK; e += 256) {
-      const int r = e / HT_BK, kk = e % HT_BK;
-      Ws[r][kk] = (n0 + r < N && k0 + kk < K) ? W[(size_t)(n0 + r) * K + k0 + kk] : zero;
-    }
-    __syncthreads();
+  for (int e = threadIdx.x; e < M * Kp; e += blockDim.x) {
+    const int r = e / Kp, k = e - r * Kp;
+    a_sh[e] = k < K ? cima_to_f32<TA>(A[(size_t)r * lda + k]) : 0.f;
+  }
+  __syncthreads();
+  const float* ar = a_sh + m * Kp;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HL_FEW_K) {
+    const int kn = min(HL_FEW_K, K - k0);
+    if (k0 > 0) {
+      if (vec && kn == HL_FEW_K) {
 #pragma unroll
-    for (int kk = 0; kk < HT_BK; kk += 16) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
-      wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b;
-      wmma::load_matrix_sync(a, &As[wm * 16][kk], HT_BK + 8);
-      wmma::load_matrix_sync(b, &Ws[wn * 16][kk], HT_BK + 8);
-      wmma::mma_sync(c, a, b, c);
+        for (int q = 0; q < HL_FEW_K / V; q++) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(wr + k0 + q * V);
+          const TA* e = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+          for (int i = 0; i < V; i++) w[q * V + i] = cima_to_f32<TA>(e[i]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < HL_FEW_K; q++) w[q] = q < kn ? cima_to_f32<TA>(wr[k0 + q]) : 0.f;
+      }
     }
-    __syncthreads();
+    // (chunks beyond the row's end were loaded as zeros, and A's row is padded with zeros to a multiple of 4)
+#pragma unroll
+    for (int q = 0; q < HL_FEW_K; q += 4) {
+      if (q < kn) {
+        const float4 a = *reinterpret_cast<const float4*>(ar + k0 + q);
+        acc = fmaf(a.x, w[q], acc);
+        acc = fmaf(a.y, w[q + 1], acc);
+        acc = fmaf(a.z, w[q + 2], acc);
+        acc = fmaf(a.w, w[q + 3], acc);
+      }
+    }
   }
-  wmma::store_matrix_sync(&Cs[warp][0][0], c, 16 + 4, wmma::mem_row_major);
-  __syncwarp();
-  for (int e = lane; e < 256; e += 32) {
-    const int r = e >> 4, cc = e & 15;
-    const int m = m0 + wm * 16 + r, n = n0 + wn * 16 + cc;
-    if (m < M && n < N) out[(size_t)m * ldo + n] = __float2bfloat16_rn(Cs[warp][r][cc]);
-  }
+  if (live) out[(size_t)m * ldo + (size_t)head * N + n] = cima_from_f32<TA>(acc);
 }
 
 // a [M, heads, K] in rows of lda, w [heads, N, K] contiguous, out [M, heads, N] in rows of ldo; all of `dtype`.
@@ -208,15 +196,17 @@ extern "C" int cima_head_linear(const void* a, const void* w, void* out, int dty
   if (lda < heads * K || ldo < heads * N) return cima_fail(CIMA_E_SIZE, "head_linear: rows of (%d, %d) do not hold %d heads of (%d, %d)", lda, ldo, heads, K, N);
   if (heads > 65535 || (M + 63) / 64 > 65535) return cima_fail(CIMA_E_SIZE, "head_linear: %d heads / %d rows exceed one launch", heads, M);
   int rc;
-  if (M <= HL_FEW_ROWS && (size_t)M * K * 4 <= 48 * 1024) {
+  if (M <= HL_FEW_ROWS && (size_t)M * (K + 3) * 4 <= 48 * 1024) {
     const dim3 grid((N + 31) / 32, heads);
-    const size_t smem = (size_t)M * K * sizeof(float);
-    if (dtype == CIMA_F32) rc = cima_launch(k_head_linear_few<float>, grid, dim3(256), smem, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo);
-    else if (dtype == CIMA_BF16) rc = cima_launch(k_head_linear_few<__nv_bfloat16>, grid, dim3(256), smem, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo);
+    const size_t smem = (size_t)M * ((K + 3) & ~3) * sizeof(float);
+    const int esz = dtype == CIMA_F32 ? 4 : 2;
+    const int vec = (((uintptr_t)w & 15) == 0 && ((size_t)K * esz) % 16 == 0) ? 1 : 0;      // every row of w starts on 16 bytes
+    if (dtype == CIMA_F32) rc = cima_launch(k_head_linear_few<float>, grid, dim3(32 * M), smem, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo, vec);
+    else if (dtype == CIMA_BF16) rc = cima_launch(k_head_linear_few<__nv_bfloat16>, grid, dim3(32 * M), smem, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo, vec);
     else return cima_fail(CIMA_E_DTYPE, "head_linear: dtype code %d is neither float32 nor bfloat16", dtype);
   } else if (dtype == CIMA_BF16) {
-    const dim3 grid((N + HT_BN - 1) / HT_BN, (M + HT_BM - 1) / HT_BM, heads);
-    rc = cima_launch(k_head_linear_mma, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo);
+    const dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
+    rc = cima_launch(k_head_linear<__nv_bfloat16>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo);
   } else if (dtype == CIMA_F32) {
     const dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
     rc = cima_launch(k_head_linear<float>, grid, dim3(256), (size_t)0, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo);

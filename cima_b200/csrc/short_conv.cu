@@ -1,5 +1,6 @@
 // A short causal convolution over time on each channel, added to its input:
-//   u[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - taps + 1 + j, c]        (zeros before a sequence's start)
+//   u[t, c] = h[t, c] + sum_{j < taps} w[j, c] * h[t - taps + 1 + j, c]        (zeros before a sequence's start)
+// (the weight is kept tap by tap, [taps, C], so that neighbouring threads read neighbouring values)
 // for the ragged rows of a step.  What lies before the step's first row of a sequence comes from the
 // sequence's state [slots, taps - 1, C]: entry k holds the input of position len - (taps - 1) + k, len being the
 // positions the sequence held before the step (zeros where that is negative: a slot's state is zeroed when it
@@ -27,7 +28,6 @@ k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restri
   const int k = ONE_ROW ? 0 : row - seq_first_row[seq];          // index of the row among the step's rows of its sequence
   const int slot = seq_slot[seq];
   TA* st = state + (size_t)slot * (taps - 1) * C + c;
-  const float* wc = w + (size_t)c * taps;
   const float cur = cima_to_f32<TA>(h[(size_t)row * C + c]);
   float acc = cur;
   float old[CONV_MAX_TAPS];
@@ -40,7 +40,7 @@ k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restri
     else if (back <= k) v = cima_to_f32<TA>(h[(size_t)(row - back) * C + c]);
     else v = cima_to_f32<TA>(st[(size_t)(taps - 1 - (back - k)) * C]);
     old[j] = v;
-    acc = fmaf(wc[j], v, acc);
+    acc = fmaf(w[(size_t)j * C + c], v, acc);
   }
   u[(size_t)row * C + c] = cima_from_f32<TA>(acc);
   if (ONE_ROW) {
@@ -52,6 +52,61 @@ k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restri
       st[(size_t)(j - 1) * C] = cima_from_f32<TA>(old[j]);
     }
   }
+}
+
+// Many rows: a thread takes 16 bytes of a row (8 bfloat16 or 4 float32 channels), so that a row of a few thousand
+// channels is read and written in whole sectors.  Needs C a multiple of that many channels.
+template <typename TA> struct ConvVec;
+template <> struct ConvVec<float> { static constexpr int N = 4; };
+template <> struct ConvVec<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename TA>
+__global__ void __launch_bounds__(CONV_THREADS)
+k_short_conv_wide(const TA* __restrict__ h, const float* __restrict__ w, const TA* __restrict__ state,
+                  const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                  TA* __restrict__ u, int C, int taps) {
+  cima_pdl_wait();
+  constexpr int V = ConvVec<TA>::N;
+  const int row = blockIdx.x;
+  const int c = (blockIdx.y * CONV_THREADS + threadIdx.x) * V;
+  if (c >= C) return;
+  const int seq = row_seq[row];
+  const int k = row - seq_first_row[seq];
+  const TA* st = state + (size_t)seq_slot[seq] * (taps - 1) * C + c;
+  float acc[V], cur[V];
+  {
+    const uint4 raw = *reinterpret_cast<const uint4*>(h + (size_t)row * C + c);
+    const TA* e = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+    for (int i = 0; i < V; i++) acc[i] = cur[i] = cima_to_f32<TA>(e[i]);
+  }
+  for (int j = 0; j < taps; j++) {
+    const int back = taps - 1 - j;
+    float v[V];
+    if (back == 0) {
+#pragma unroll
+      for (int i = 0; i < V; i++) v[i] = cur[i];
+    } else {
+      const TA* src = back <= k ? h + (size_t)(row - back) * C + c : st + (size_t)(taps - 1 - (back - k)) * C;
+      const uint4 raw = *reinterpret_cast<const uint4*>(src);
+      const TA* e = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+      for (int i = 0; i < V; i++) v[i] = cima_to_f32<TA>(e[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < V; i += 4) {
+      const float4 ww = *reinterpret_cast<const float4*>(w + (size_t)j * C + c + i);
+      acc[i] = fmaf(ww.x, v[i], acc[i]);
+      acc[i + 1] = fmaf(ww.y, v[i + 1], acc[i + 1]);
+      acc[i + 2] = fmaf(ww.z, v[i + 2], acc[i + 2]);
+      acc[i + 3] = fmaf(ww.w, v[i + 3], acc[i + 3]);
+    }
+  }
+  uint4 outv;
+  TA* o = reinterpret_cast<TA*>(&outv);
+#pragma unroll
+  for (int i = 0; i < V; i++) o[i] = cima_from_f32<TA>(acc[i]);
+  *reinterpret_cast<uint4*>(u + (size_t)row * C + c) = outv;
 }
 
 template <typename TA>
@@ -78,7 +133,7 @@ k_short_conv_state(const TA* __restrict__ h, TA* __restrict__ state, const int* 
   }
 }
 
-// h, u [T, C] and state [slots, taps - 1, C] of one dtype; w [C, taps] float32.  one_row != 0: row r is sequence r's only row.
+// h, u [T, C] and state [slots, taps - 1, C] of one dtype; w [taps, C] float32.  one_row != 0: row r is sequence r's only row.
 extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* state, const int* row_seq, const int* seq_slot,
                                const int* seq_first_row, void* u, int T, int n_seqs, int C, int taps, int one_row,
                                cudaStream_t stream) {
@@ -89,9 +144,13 @@ extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* s
   if (taps > 1 && !state) return cima_fail(CIMA_E_ARG, "short_conv: more than one tap needs the sequences' state");
   const dim3 block(CONV_THREADS);
   const unsigned cy = (unsigned)((C + CONV_THREADS - 1) / CONV_THREADS);
+  // 16-byte accesses: the rows of h, u and the state must all start on 16 bytes
+  const int per16 = dtype == CIMA_F32 ? 4 : 8;
+  const bool wide = C % per16 == 0 && (((uintptr_t)h | (uintptr_t)u | (uintptr_t)state | (uintptr_t)w) & 15) == 0;
 #define RUN(TA) { \
     int rc_; \
     if (one_row) rc_ = cima_launch(k_short_conv<TA, true>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
+    else if (wide) rc_ = cima_launch(k_short_conv_wide<TA>, dim3(T, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
     else rc_ = cima_launch(k_short_conv<TA, false>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
     if (rc_) return rc_; \
     if (!one_row && taps > 1) { rc_ = cima_launch(k_short_conv_state<TA>, dim3(n_seqs, cy), block, (size_t)0, stream, 1, (const TA*)h, (TA*)state, seq_slot, seq_first_row, C, taps); if (rc_) return rc_; } }

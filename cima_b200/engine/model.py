@@ -298,11 +298,14 @@ class Model:
         x, info = self.depth.start(stack), None
         for site, block in enumerate(order):
             block.forward(x, batch, self.cache, site, info, None)
+            conv = None
             if site + 1 < len(order):
                 nxt = getattr(order[site + 1], "mixer_norm", None)
+                if getattr(order[site + 1], "conv", None) is not None:
+                    conv = (order[site + 1].conv, batch, self.cache, site + 1)
             else:
                 nxt = self.final_norm if batch.want_all_in_order else None
-            x, info = self.depth.after(stack, site, nxt)
+            x, info = self.depth.after(stack, site, nxt, conv)
         return self.project(x, batch, info)
 
     def project(self, x: torch.Tensor, batch: StepBatch, info=None) -> torch.Tensor:

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 21
+ABI_VERSION = 22
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -74,7 +74,7 @@ _SIGNATURES = {
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                  _f, _i, _vp, _i, _vp],
     "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp],
     "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
@@ -599,13 +599,13 @@ class Kernels:
 
     # ------------------------------------------------------------------ short convolution, depth average, latents
     def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], batch, out: torch.Tensor) -> None:
-        """out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j] per channel, causal within each sequence of the
+        """out[t] = h[t] + sum_j w[j, :] * h[t - taps + 1 + j] per channel, causal within each sequence of the
         step; what lies before the step's rows comes from ``state`` [slots, taps - 1, C] (the sequences' last
-        inputs), which is brought up to date.  ``w`` [C, taps] float32; h, out, state of one dtype."""
+        inputs), which is brought up to date.  ``w`` [taps, C] float32 (tap by tap); h, out, state of one dtype."""
         self._need(h, "h", None, 2); self._need(w, "w", torch.float32, 2); self._need(out, "out", h.dtype, 2)
         T, C = h.shape
-        taps = w.shape[1]
-        if w.shape[0] != C or out.shape != h.shape:
+        taps = w.shape[0]
+        if w.shape[1] != C or out.shape != h.shape:
             raise KernelError(f"short_conv: h {tuple(h.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
         if taps > 1:
             self._need(state, "state", h.dtype, 3)
@@ -620,9 +620,11 @@ class Kernels:
             self.launches += 1
 
     def depth_average(self, stack: torch.Tensor, n: int, a: torch.Tensor, x: torch.Tensor,
-                      w: Optional[torch.Tensor] = None, eps: float = 0.0, y: Optional[torch.Tensor] = None) -> None:
+                      w: Optional[torch.Tensor] = None, eps: float = 0.0, y: Optional[torch.Tensor] = None,
+                      conv=None) -> None:
         """x = sum_{j < n} a[j] * stack[j] (float32 [planes, T, H]); with ``w`` also y = RMSNorm(x; w, eps).
-        ``x`` may be a plane of ``stack`` beyond the first n."""
+        ``x`` may be a plane of ``stack`` beyond the first n.  ``conv = (cw, state, seq_slot, u)``, for a step of one
+        row a sequence: also u = ``short_conv`` of y (weights cw [taps, H], the sequences' state brought up to date)."""
         self._need(stack, "stack", torch.float32, 3); self._need(a, "a", torch.float32, 1); self._need(x, "x", torch.float32, 2)
         P, T, H = stack.shape
         if not (1 <= n <= P) or a.numel() != n or tuple(x.shape) != (T, H):
@@ -633,10 +635,23 @@ class Kernels:
             self._need(w, "w", torch.float32, 1); self._need(y, "y", None, 2)
             if w.numel() != H or tuple(y.shape) != (T, H):
                 raise KernelError(f"depth_average: w {tuple(w.shape)} / y {tuple(y.shape)} do not fit {(T, H)}")
-        if not self._admit("depth_average", T * H * (4 * (n + 1) + (y.element_size() if y is not None else 0))): return
+        extra = (None, 0, None, None, None)
+        if conv is not None:
+            cw, state, seq_slot, u = conv
+            self._need(cw, "cw", torch.float32, 2); self._need(seq_slot, "seq_slot", torch.int32, 1)
+            taps = cw.shape[0]
+            if y is None or cw.shape[1] != H or seq_slot.numel() != T or tuple(u.shape) != (T, H) or u.dtype is not y.dtype:
+                raise KernelError("depth_average: the convolution goes with the norm, one row a sequence, and an output like y")
+            self._need(u, "u", y.dtype, 2)
+            if taps > 1:
+                self._need(state, "state", y.dtype, 3)
+                if tuple(state.shape[1:]) != (taps - 1, H):
+                    raise KernelError(f"depth_average: state is {tuple(state.shape)}, expected [slots, {taps - 1}, {H}]")
+            extra = (cw.data_ptr(), taps, _ptr(state if taps > 1 else None), seq_slot.data_ptr(), u.data_ptr())
+        if not self._admit("depth_average", T * H * (4 * (n + 1) + ((2 if conv else 1) * y.element_size() if y is not None else 0))): return
         self._check(self.lib.cima_depth_average(stack.data_ptr(), T * H, a.data_ptr(), n, x.data_ptr(), _ptr(w), _ptr(y),
-                                                dtype_code(y.dtype) if y is not None else F32, T, H, eps, self._stream()),
-                    "depth_average")
+                                                dtype_code(y.dtype) if y is not None else F32, T, H, eps, *extra,
+                                                self._stream()), "depth_average")
 
     def latent_append(self, raw: torch.Tensor, g: torch.Tensor, eps: float, kv, batch) -> None:
         """c = RMSNorm(raw; g, eps) per row, written to the row's position in the layer's pages (one plane, one
@@ -660,6 +675,11 @@ class Kernels:
         if a.dim() != 2 or a.stride(1) != 1 or a.shape[1] != heads * K or tuple(out.shape) != (T, heads * N):
             raise KernelError(f"head_linear: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
         if not self._admit("head_linear", (w.numel() + a.numel() + out.numel()) * a.element_size(), 2.0 * T * heads * N * K): return
+        if a.dtype is torch.bfloat16 and T > 8:
+            # many bfloat16 rows: the library's batched product, as for the other products of more than 8 rows
+            self.library_launches += 1
+            torch.bmm(a.view(T, heads, K).transpose(0, 1), w.transpose(1, 2), out=out.view(T, heads, N).transpose(0, 1))
+            return
         self._check(self.lib.cima_head_linear(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K,
                                               a.stride(0), out.stride(0), self._stream()), "head_linear")
 

@@ -162,7 +162,12 @@ class ParallelBlock:
             h = info.h                                             # the rows came normalised already
         else:
             h = self.mixer_norm(x)
-        u = self.conv.forward(h, batch, cache, site) if self.conv is not None else h
+        if self.conv is None:
+            u = h
+        elif info is not None and getattr(info, "conv", None) is self.conv and info.u is not None:
+            u = info.u                                             # ... and convolved, the state moved on
+        else:
+            u = self.conv.forward(h, batch, cache, site)
         self.mixer.forward(u, x, batch, cache, site)
         if self.feed_forward is not None:
             self.feed_forward.forward(h, x, batch)

@@ -46,14 +46,25 @@ class DepthAverage:
         stack[1].copy_(stack[0])
         return stack[1]
 
-    def after(self, stack: torch.Tensor, site: int, next_norm=None):
+    def after(self, stack: torch.Tensor, site: int, next_norm=None, next_conv=None):
         """The input of the site after ``site`` (or of the final norm) and, where the norm that reads it is a plain
-        RMSNorm, that norm's output with it."""
+        RMSNorm, that norm's output with it.  ``next_conv = (conv, batch, cache, site)``: the short convolution that
+        reads that norm's output; in a step of one row a sequence it runs in the same kernel, and its result travels
+        with the rows (``RowsInfo.conv`` / ``.u``)."""
         x = stack[site + 2]
         if (next_norm is not None and getattr(next_norm, "weight", None) is not None
                 and next_norm.spec.kind == "rmsnorm" and next_norm.spec.size == x.shape[1]):
             h = self.rt.empty(*x.shape)
-            self.rt.kernels.depth_average(stack, site + 2, self.weights[site], x, next_norm.weight, next_norm.spec.eps, h)
-            return x, RowsInfo(norm=next_norm, h=h)
+            info = RowsInfo(norm=next_norm, h=h)
+            fused = None
+            if next_conv is not None and next_conv[1].n_rows == next_conv[1].n_seqs:
+                conv, batch, cache, conv_site = next_conv
+                u = self.rt.empty(*x.shape)
+                state = cache.state[conv.state_name(conv_site)] if conv.spec.taps > 1 else None
+                fused = (conv.weight, state, batch.seq_slot, u)
+                info.conv, info.u = conv, u
+            self.rt.kernels.depth_average(stack, site + 2, self.weights[site], x, next_norm.weight, next_norm.spec.eps, h,
+                                          conv=fused)
+            return x, info
         self.rt.kernels.depth_average(stack, site + 2, self.weights[site], x)
         return x, None

@@ -19,6 +19,7 @@ class RowsInfo:
     def __init__(self, ssq=None, norm=None, h=None, xw=None, xw_norm=None):
         self.ssq, self.norm, self.h = ssq, norm, h
         self.xw, self.xw_norm = xw, xw_norm       # rows times the weight of ``xw_norm``, bf16 (goes with ssq)
+        self.conv, self.u = None, None            # a short convolution that has already read ``h``, and its output
 
 
 class NormedInput:

@@ -5,7 +5,8 @@
 A sequence's newest ``taps - 1`` inputs travel with it as state (``StateRequest``: [slots, taps - 1, channels] in the
 activations' dtype, zeroed when a slot opens, which is exactly the zeros before the start), so a step's first
 rows find their predecessors whether the sequence starts, goes on by one token or by many.  The weight
-[channels, taps] is kept in float32; products and sums are float32.
+[channels, taps] is kept in float32 and tap by tap ([taps, channels]: neighbouring threads read neighbouring
+values); products and sums are float32.
 """
 from __future__ import annotations
 
@@ -28,10 +29,10 @@ class ShortConv:
         return {name: TensorSpec((self.spec.channels, self.spec.taps), std=0.2)}
 
     def load(self, tensors, name: str) -> None:
-        self.weight = self.rt.vector(tensors[name])
+        self.weight = self.rt.vector(tensors[name]).t().contiguous()          # [taps, channels]
 
     def state(self, name: str) -> Dict[str, torch.Tensor]:
-        return {name: self.weight}
+        return {name: self.weight.t()}
 
     def nbytes(self) -> int:
         return self.weight.numel() * 4

@@ -215,7 +215,7 @@ class ReferenceKernels:
 
 # ---------------------------------------------------------------------- short convolution, depth average, latents
 def _short_conv(self, h, w, state, batch, out):
-    taps = w.shape[1]
+    taps = w.shape[0]
     first = batch.seq_first_row
     hc = h.to(self.compute)
     for s in range(batch.n_seqs):
@@ -226,19 +226,29 @@ def _short_conv(self, h, w, state, batch, out):
         n = hi - lo
         acc = hc[lo:hi].clone()
         for j in range(taps):
-            acc = acc + w[:, j].to(self.compute) * line[j:j + n]
+            acc = acc + w[j].to(self.compute) * line[j:j + n]
         out[lo:hi] = acc.to(out.dtype)
         if taps > 1:
             state[slot] = line[n:].to(state.dtype)
 
 
-def _depth_average(self, stack, n, a, x, w=None, eps=0.0, y=None):
+def _depth_average(self, stack, n, a, x, w=None, eps=0.0, y=None, conv=None):
     acc = torch.zeros_like(x)
     for j in range(n):
         acc = acc + a[j] * stack[j]
     x.copy_(acc)
     if w is not None:
         self.rmsnorm(x, w, eps, y)
+    if conv is not None:
+        cw, state, seq_slot, u = conv
+        taps = cw.shape[0]
+        for r in range(x.shape[0]):
+            slot = int(seq_slot[r])
+            past = state[slot].to(self.compute) if taps > 1 else y[:0].to(self.compute)
+            line = torch.cat([past, y[r:r + 1].to(self.compute)])
+            u[r] = (y[r].to(self.compute) + (cw.to(self.compute) * line).sum(dim=0)).to(u.dtype)
+            if taps > 1:
+                state[slot] = line[1:].to(state.dtype)
 
 
 def _latent_append(self, raw, g, eps, kv, batch):

@@ -58,7 +58,7 @@ def test_short_conv_in_pieces(taps, C, dtype):
         b = entries_batch(counts, pos, slots)
         h = torch.cat([hs[i][pos[i]:pos[i] + c] for i, c in enumerate(counts)]).to(DEV)
         out = torch.empty_like(h)
-        K().short_conv(h, w.to(DEV), state if taps > 1 else None, b, out)
+        K().short_conv(h, w.t().contiguous().to(DEV), state if taps > 1 else None, b, out)
         r = 0
         for i, c in enumerate(counts):
             got[i].append(out[r:r + c].float().cpu()); r += c; pos[i] += c
@@ -86,6 +86,27 @@ def test_depth_average_with_and_without_the_norm(n, T, H, dtype):
     assert (y.cpu().double() - wy).abs().max().item() < (1e-5 if dtype == "float32" else 4e-2)
     K().depth_average(sd, n, a.to(DEV), sd[n + 1])
     assert torch.equal(sd[n + 1], sd[n])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps,H", [(1, 40), (2, 96), (4, 1536)])
+def test_depth_average_with_the_convolution_of_a_decode_step(taps, H, dtype):
+    """One row a sequence: average, norm, convolution and the state's update as one launch give what the three give."""
+    g = torch.Generator().manual_seed(taps)
+    n, T = 3, 5
+    stack = torch.randn(n + 1, T, H, generator=g).to(DEV)
+    a, w, cw = torch.randn(n, generator=g).to(DEV), (1 + 0.1 * torch.randn(H, generator=g)).to(DEV), torch.randn(taps, H, generator=g).to(DEV)
+    slots = [3, 0, 6, 1, 4]
+    state = torch.randn(7, max(taps - 1, 1), H, generator=g).to(DT[dtype]).to(DEV)[:, :taps - 1].contiguous()
+    b = entries_batch([1] * T, [9] * T, slots)
+    y1, u1, s1 = torch.empty(T, H, dtype=DT[dtype], device=DEV), torch.empty(T, H, dtype=DT[dtype], device=DEV), state.clone()
+    K().depth_average(stack, n, a, stack[n], w, 1e-5, y1)
+    K().short_conv(y1, cw, s1 if taps > 1 else None, b, u1)
+    y2, u2, s2 = torch.empty_like(y1), torch.empty_like(u1), state.clone()
+    K().depth_average(stack, n, a, stack[n], w, 1e-5, y2, conv=(cw, s2 if taps > 1 else None, b.seq_slot, u2))
+    assert torch.equal(y1, y2) and torch.equal(u1, u2) and torch.equal(s1, s2)
+    if taps > 1:
+        assert not torch.equal(s1, state) and torch.equal(s1[2], state[2])      # slots 2 and 5 belong to nobody in the step
 
 
 def latent_cache(R, dtype, n_pages=12, slots=4):
