@@ -62,9 +62,10 @@ constexpr int MAX_SPLITS = 64;
 // Pages in flight per block: as many as fill about 104 KB of shared memory with their padded tiles, so that two blocks
 // fit an SM whatever the head size and hold the same bytes in flight (3 pages of 34 KB at head_dim 128, 5 of 18 KB at
 // 64; with 3 at every head size a block of 64-wide heads drew half the bandwidth).
-__host__ __device__ constexpr int decode_stages(int hd) {
-  const int n = (104 * 1024) / (2 * PS * (hd + 8) * 2);
-  return n < 3 ? 3 : (n > 8 ? 8 : n);
+// Pages of one plane (a shared vector that is key and value at once) are half the bytes, so twice as many fit.
+__host__ __device__ constexpr int decode_stages(int hd, int planes = 2) {
+  const int n = (104 * 1024) / (planes * PS * (hd + 8) * 2);
+  return n < 3 ? 3 : (n > 8 * (3 - planes) ? 8 * (3 - planes) : n);
 }
 
 // The splits that get pages of a sequence with ``len`` positions: at most one per page of the visible keys.
@@ -76,7 +77,7 @@ __device__ __forceinline__ int live_splits(int len, int window, int n_splits) {
 // early: the sequence's lengths, slots and block table, and every page before the one that holds the newest
 // position, are not written by the kernel launched just before this one (the q/k/v projection with its cache
 // append writes the newest position only); the first pages are then fetched before the wait on that kernel.
-template <int HD>
+template <int HD, int PLANES>
 __global__ void __launch_bounds__(WARPS * 32)
 k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfloat16* __restrict__ cache,
                    CimaPaged pg, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
@@ -86,9 +87,9 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
   constexpr int TILE = PS * ROW;                      // elements of one K or V tile
   constexpr int KSTEPS = HD / 16, NTILES = HD / 8;
-  constexpr int STAGES = decode_stages(HD);
+  constexpr int STAGES = decode_stages(HD, PLANES);
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [STAGES][K|V][PS][ROW]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [STAGES][K|V, or the one shared tile][PS][ROW]
 
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / mtiles, mt = blockIdx.y % mtiles;
@@ -121,14 +122,14 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   auto issue = [&](int page, int stage) {
     // one page: K then V, each [PS][HD] contiguous in the cache -> padded rows in shared memory
     // (with one plane the page's vectors are keys and values at once: one copy, and the V tile is the K tile)
-    const __nv_bfloat16* src = cache + (((size_t)page * pg.planes) * pg.kv_heads + kvh) * (size_t)(PS * HD);
+    const __nv_bfloat16* src = cache + (((size_t)page * PLANES) * pg.kv_heads + kvh) * (size_t)(PS * HD);
     const size_t vofs = (size_t)pg.kv_heads * PS * HD;
-    __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
+    __nv_bfloat16* dst = tiles + (size_t)stage * PLANES * TILE;
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
     for (int c = threadIdx.x; c < PS * CPR; c += WARPS * 32) {
       const int r = c / CPR, cc = c % CPR;
       cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
-      if (pg.planes == 2) cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+      if (PLANES == 2) cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
     }
   };
 
@@ -179,8 +180,8 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     if (p + STAGES - 1 < p1) issue(page_next, (p - p0 + STAGES - 1) % STAGES);
     cp_async_commit();
     if (p + STAGES < p1) page_next = page_of(p + STAGES);
-    const __nv_bfloat16* Kt = tiles + (size_t)stage * 2 * TILE;
-    const __nv_bfloat16* Vt = pg.planes == 2 ? Kt + TILE : Kt;
+    const __nv_bfloat16* Kt = tiles + (size_t)stage * PLANES * TILE;
+    const __nv_bfloat16* Vt = PLANES == 2 ? Kt + TILE : Kt;
     const int kw = warp * KEYS_PER_WARP;              // this warp's keys within the page
 
     // S = Q K^T for 16 keys: two n-tiles of 8 keys
@@ -343,13 +344,13 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
   }
 }
 
-template <int HD>
+template <int HD, int PLANES>
 int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, const int* seq_slot, const int* seq_len,
                   float* part_o, float* part_ml, void* out, int ldo, int B, int nh, int nkv, float scale, int window,
                   int n_splits, int early, cudaStream_t stream) {
-  auto kern = k_attention_decode<HD>;
-  constexpr int STAGES = decode_stages(HD);
-  const size_t tiles = (size_t)STAGES * 2 * PS * (HD + 8) * sizeof(__nv_bfloat16);
+  auto kern = k_attention_decode<HD, PLANES>;
+  constexpr int STAGES = decode_stages(HD, PLANES);
+  const size_t tiles = (size_t)STAGES * PLANES * PS * (HD + 8) * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)WARPS * 16 * (HD + 2) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
   static bool raised = false;
@@ -389,7 +390,8 @@ extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache,
   if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
   if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd, planes};
-#define CASE(H) case H: return launch_decode<H>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, stream)
+#define CASE(H) case H: return planes == 2 ? launch_decode<H, 2>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, stream) \
+                                          : launch_decode<H, 1>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }

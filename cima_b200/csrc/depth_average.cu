@@ -53,15 +53,15 @@ k_depth_average(const float* __restrict__ stack, size_t plane, const float* __re
   }
 }
 
-// The same for rows of at most 2048 values with at most 4 taps, which is every decode step of the usual sizes: a
-// thread keeps its (at most 8) values of the row in registers between the sum and the norm, and reads everything
+// The same for rows of at most 8192 values with at most 4 taps, which is every decode step of the usual sizes: a
+// block of 256, 512 or 1024 threads by the row's width, a thread keeps its (at most 8) values of the row in registers between the sum and the norm, and reads everything
 // that does not depend on the norm (the convolution's weights and the sequence's last inputs) before it waits
 // for the row's sum of squares, all loads before all stores: the kernel is a chain of memory round trips, and
 // this leaves three of them.  Same operations in the same order as the general kernel: the same bits.
 constexpr int DA_EPT = 8, DA_PAST = 3;
 
-template <typename TA, bool CONV>
-__global__ void __launch_bounds__(DA_THREADS)
+template <typename TA, bool CONV, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 k_depth_average_row(const float* __restrict__ stack, size_t plane, const float* __restrict__ a, int n,
                     float* __restrict__ x, const float* __restrict__ w, TA* __restrict__ y, int H, float eps,
                     const float* __restrict__ cw, int taps, TA* __restrict__ state, const int* __restrict__ seq_slot,
@@ -69,7 +69,7 @@ k_depth_average_row(const float* __restrict__ stack, size_t plane, const float* 
   cima_pdl_wait();
   __shared__ float red[32];
   __shared__ float fac[DA_MAX];
-  for (int j = threadIdx.x; j < n; j += DA_THREADS) fac[j] = a[j];
+  for (int j = threadIdx.x; j < n; j += THREADS) fac[j] = a[j];
   __syncthreads();
   const size_t row = (size_t)blockIdx.x * H;
   float xv[DA_EPT], wv[DA_EPT];
@@ -80,14 +80,14 @@ k_depth_average_row(const float* __restrict__ stack, size_t plane, const float* 
     const float* src = stack + (size_t)j * plane + row;
 #pragma unroll
     for (int e = 0; e < DA_EPT; e++) {
-      const int i = threadIdx.x + e * DA_THREADS;
+      const int i = threadIdx.x + e * THREADS;
       if (i < H) xv[e] = fmaf(f, src[i], xv[e]);
     }
   }
   float ss = 0.f;
 #pragma unroll
   for (int e = 0; e < DA_EPT; e++) {
-    const int i = threadIdx.x + e * DA_THREADS;
+    const int i = threadIdx.x + e * THREADS;
     if (i < H) { x[row + i] = xv[e]; ss += xv[e] * xv[e]; wv[e] = w[i]; }
   }
   TA old[DA_EPT][DA_PAST];
@@ -97,7 +97,7 @@ k_depth_average_row(const float* __restrict__ stack, size_t plane, const float* 
     st = state + (size_t)seq_slot[blockIdx.x] * (taps - 1) * H;
 #pragma unroll
     for (int e = 0; e < DA_EPT; e++) {
-      const int i = threadIdx.x + e * DA_THREADS;
+      const int i = threadIdx.x + e * THREADS;
       if (i < H) {
 #pragma unroll
         for (int j = 0; j < DA_PAST; j++)
@@ -110,7 +110,7 @@ k_depth_average_row(const float* __restrict__ stack, size_t plane, const float* 
   const float inv = 1.0f / sqrtf(total / (float)H + eps);
 #pragma unroll
   for (int e = 0; e < DA_EPT; e++) {
-    const int i = threadIdx.x + e * DA_THREADS;
+    const int i = threadIdx.x + e * THREADS;
     if (i < H) {
       const TA yv = cima_from_f32<TA>(xv[e] * inv * wv[e]);
       y[row + i] = yv;
@@ -145,16 +145,21 @@ extern "C" int cima_depth_average(const float* stack, long long plane, const flo
   if (cw && (!w || !u || !seq_slot || taps < 1 || taps > 16 || (taps > 1 && !state)))
     return cima_fail(CIMA_E_ARG, "depth_average: the convolution needs the norm, 1..16 taps, the sequences' slots and state, and its output");
   int rc;
-  const bool row_kernel = w && H <= DA_EPT * DA_THREADS && (!cw || taps <= DA_PAST + 1);
+  const bool row_kernel = w && H <= DA_EPT * 1024 && (!cw || taps <= DA_PAST + 1);
+  const int threads = H <= DA_EPT * 256 ? 256 : (H <= DA_EPT * 512 ? 512 : 1024);
 #define DA_ARGS(TA) stack, (size_t)plane, a, n, x, w, (TA*)y, H, eps, cw, taps, (TA*)state, seq_slot, (TA*)u
+#define DA_ROW(TA, C) \
+  (threads == 256 ? cima_launch(k_depth_average_row<TA, C, 256>, dim3(T), dim3(256), (size_t)0, stream, 1, DA_ARGS(TA)) \
+   : threads == 512 ? cima_launch(k_depth_average_row<TA, C, 512>, dim3(T), dim3(512), (size_t)0, stream, 1, DA_ARGS(TA)) \
+                    : cima_launch(k_depth_average_row<TA, C, 1024>, dim3(T), dim3(1024), (size_t)0, stream, 1, DA_ARGS(TA)))
 #define DA_RUN(TA) \
-  (row_kernel ? (cw ? cima_launch(k_depth_average_row<TA, true>, dim3(T), dim3(DA_THREADS), (size_t)0, stream, 1, DA_ARGS(TA)) \
-                    : cima_launch(k_depth_average_row<TA, false>, dim3(T), dim3(DA_THREADS), (size_t)0, stream, 1, DA_ARGS(TA))) \
+  (row_kernel ? (cw ? DA_ROW(TA, true) : DA_ROW(TA, false)) \
               : cima_launch(k_depth_average<TA>, dim3(T), dim3(DA_THREADS), (size_t)0, stream, 1, DA_ARGS(TA)))
   if (!w || y_dtype == CIMA_F32) rc = DA_RUN(float);
   else if (y_dtype == CIMA_BF16) rc = DA_RUN(__nv_bfloat16);
   else return cima_fail(CIMA_E_DTYPE, "depth_average: dtype code %d is neither float32 nor bfloat16", y_dtype);
 #undef DA_RUN
+#undef DA_ROW
 #undef DA_ARGS
   if (rc) return rc;
   return cima_launch_result();

@@ -109,6 +109,95 @@ k_short_conv_wide(const TA* __restrict__ h, const float* __restrict__ w, const T
   *reinterpret_cast<uint4*>(u + (size_t)row * C + c) = outv;
 }
 
+// Many rows and at most 4 taps: a thread takes 16 bytes of channels through CONV_ROWS (8, 4 or 2) consecutive rows, keeps the
+// weights of its channels and the last taps - 1 inputs in registers, and so reads every input once (the block's
+// first rows again, as the rows before them) instead of taps times, the chunk's eight loads all in flight at once.  Where a row is not the successor of the row
+// before it in its own sequence (the chunk's first row, a sequence's first rows) its past is fetched as in the
+// kernel above.  Same products in the same order: the same bits.
+constexpr int CONV_FEW_TAPS = 4;
+
+template <typename TA, int CONV_ROWS>
+__global__ void __launch_bounds__(CONV_THREADS)
+k_short_conv_rows(const TA* __restrict__ h, const float* __restrict__ w, const TA* __restrict__ state,
+                  const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                  TA* __restrict__ u, int T, int C, int taps) {
+  cima_pdl_wait();
+  constexpr int V = ConvVec<TA>::N;
+  const int c = (blockIdx.y * CONV_THREADS + threadIdx.x) * V;
+  if (c >= C) return;
+  float wv[CONV_FEW_TAPS][V], past[CONV_FEW_TAPS - 1][V];       // past[b - 1]: the input b positions back
+#pragma unroll
+  for (int j = 0; j < CONV_FEW_TAPS; j++)
+    if (j < taps) {
+#pragma unroll
+      for (int i = 0; i < V; i += 4) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + (size_t)j * C + c + i);
+        wv[j][i] = ww.x; wv[j][i + 1] = ww.y; wv[j][i + 2] = ww.z; wv[j][i + 3] = ww.w;
+      }
+    }
+  const int r0 = blockIdx.x * CONV_ROWS, r1 = min(T, r0 + CONV_ROWS);
+  uint4 rows[CONV_ROWS];                                        // all of the chunk's inputs are requested at once
+#pragma unroll
+  for (int r = 0; r < CONV_ROWS; r++)
+    if (r0 + r < r1) rows[r] = *reinterpret_cast<const uint4*>(h + (size_t)(r0 + r) * C + c);
+  int prev_seq = -1;
+#pragma unroll
+  for (int r = 0; r < CONV_ROWS; r++) {
+    const int row = r0 + r;
+    if (row >= r1) break;
+    const int seq = row_seq[row];
+    const int k = row - seq_first_row[seq];
+    float cur[V];
+    {
+      const TA* e = reinterpret_cast<const TA*>(&rows[r]);
+#pragma unroll
+      for (int i = 0; i < V; i++) cur[i] = cima_to_f32<TA>(e[i]);
+    }
+    if (seq != prev_seq || k < taps - 1) {
+      // the past from scratch: rows of the step where they are the sequence's, its state before that
+      const TA* st = state + (size_t)seq_slot[seq] * (taps - 1) * C + c;
+#pragma unroll
+      for (int b = 1; b < CONV_FEW_TAPS; b++)
+        if (b < taps) {
+          const TA* src = b <= k ? h + (size_t)(row - b) * C + c : st + (size_t)(taps - 1 - (b - k)) * C;
+          const uint4 raw = *reinterpret_cast<const uint4*>(src);
+          const TA* e = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+          for (int i = 0; i < V; i++) past[b - 1][i] = cima_to_f32<TA>(e[i]);
+        }
+      prev_seq = seq;
+    }
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; i++) acc[i] = cur[i];
+#pragma unroll
+    for (int j = 0; j < CONV_FEW_TAPS; j++)
+      if (j < taps) {
+        const int back = taps - 1 - j;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+          float v = cur[i];
+#pragma unroll
+          for (int b = 1; b < CONV_FEW_TAPS; b++)
+            if (b == back) v = past[b - 1][i];
+          acc[i] = fmaf(wv[j][i], v, acc[i]);
+        }
+      }
+    uint4 outv;
+    TA* o = reinterpret_cast<TA*>(&outv);
+#pragma unroll
+    for (int i = 0; i < V; i++) o[i] = cima_from_f32<TA>(acc[i]);
+    *reinterpret_cast<uint4*>(u + (size_t)row * C + c) = outv;
+    // this row becomes the next one's nearest past
+#pragma unroll
+    for (int b = CONV_FEW_TAPS - 1; b >= 2; b--)
+#pragma unroll
+      for (int i = 0; i < V; i++) past[b - 1][i] = past[b - 2][i];
+#pragma unroll
+    for (int i = 0; i < V; i++) past[0][i] = cur[i];
+  }
+}
+
 template <typename TA>
 __global__ void __launch_bounds__(CONV_THREADS)
 k_short_conv_state(const TA* __restrict__ h, TA* __restrict__ state, const int* __restrict__ seq_slot,
@@ -134,9 +223,10 @@ k_short_conv_state(const TA* __restrict__ h, TA* __restrict__ state, const int* 
 }
 
 // h, u [T, C] and state [slots, taps - 1, C] of one dtype; w [taps, C] float32.  one_row != 0: row r is sequence r's only row.
+// rows_per_thread: 0, or how many consecutive rows a thread of the many-row kernel walks (the result does not depend on it).
 extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* state, const int* row_seq, const int* seq_slot,
                                const int* seq_first_row, void* u, int T, int n_seqs, int C, int taps, int one_row,
-                               cudaStream_t stream) {
+                               int rows_per_thread, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (taps < 1 || taps > CONV_MAX_TAPS) return cima_fail(CIMA_E_SIZE, "short_conv: %d taps are outside 1..%d", taps, CONV_MAX_TAPS);
   if (C <= 0 || n_seqs <= 0) return cima_fail(CIMA_E_SIZE, "short_conv: %d channels and %d sequences must be positive", C, n_seqs);
@@ -147,9 +237,17 @@ extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* s
   // 16-byte accesses: the rows of h, u and the state must all start on 16 bytes
   const int per16 = dtype == CIMA_F32 ? 4 : 8;
   const bool wide = C % per16 == 0 && (((uintptr_t)h | (uintptr_t)u | (uintptr_t)state | (uintptr_t)w) & 15) == 0;
+  // rows a thread walks: as many (8, 4, 2) as still leave every SM its full count of threads; else one (the kernel above)
+  const long long cells = (long long)T * (C / per16);
+  int rows_each = cells >= 8ll * 148 * 2048 ? 8 : (cells >= 4ll * 148 * 2048 ? 4 : (cells >= 2ll * 148 * 2048 ? 2 : 1));
+  if (rows_per_thread == 1 || rows_per_thread == 2 || rows_per_thread == 4 || rows_per_thread == 8) rows_each = rows_per_thread;
+  else if (rows_per_thread != 0) return cima_fail(CIMA_E_ARG, "short_conv: %d rows a thread; 0 (chosen here), 1, 2, 4 or 8 are possible", rows_per_thread);
 #define RUN(TA) { \
     int rc_; \
     if (one_row) rc_ = cima_launch(k_short_conv<TA, true>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
+    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 8) rc_ = cima_launch(k_short_conv_rows<TA, 8>, dim3((T + 7) / 8, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps); \
+    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 4) rc_ = cima_launch(k_short_conv_rows<TA, 4>, dim3((T + 3) / 4, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps); \
+    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 2) rc_ = cima_launch(k_short_conv_rows<TA, 2>, dim3((T + 1) / 2, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps); \
     else if (wide) rc_ = cima_launch(k_short_conv_wide<TA>, dim3(T, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
     else rc_ = cima_launch(k_short_conv<TA, false>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
     if (rc_) return rc_; \

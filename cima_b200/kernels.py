@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 22
+ABI_VERSION = 23
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -73,7 +73,7 @@ _SIGNATURES = {
     "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                  _f, _i, _vp, _i, _vp],
-    "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp],
     "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -598,7 +598,8 @@ class Kernels:
         return t
 
     # ------------------------------------------------------------------ short convolution, depth average, latents
-    def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], batch, out: torch.Tensor) -> None:
+    def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], batch, out: torch.Tensor,
+                   rows_per_thread: int = 0) -> None:
         """out[t] = h[t] + sum_j w[j, :] * h[t - taps + 1 + j] per channel, causal within each sequence of the
         step; what lies before the step's rows comes from ``state`` [slots, taps - 1, C] (the sequences' last
         inputs), which is brought up to date.  ``w`` [taps, C] float32 (tap by tap); h, out, state of one dtype."""
@@ -615,7 +616,8 @@ class Kernels:
         if not self._admit("short_conv", 2 * T * C * h.element_size()): return
         self._check(self.lib.cima_short_conv(h.data_ptr(), dtype_code(h.dtype), w.data_ptr(), _ptr(state if taps > 1 else None),
                                              batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_first_row.data_ptr(),
-                                             out.data_ptr(), T, batch.n_seqs, C, taps, int(one_row), self._stream()), "short_conv")
+                                             out.data_ptr(), T, batch.n_seqs, C, taps, int(one_row), rows_per_thread,
+                                             self._stream()), "short_conv")
         if not one_row and taps > 1:
             self.launches += 1
 

@@ -214,7 +214,7 @@ class ReferenceKernels:
 
 
 # ---------------------------------------------------------------------- short convolution, depth average, latents
-def _short_conv(self, h, w, state, batch, out):
+def _short_conv(self, h, w, state, batch, out, rows_per_thread=0):
     taps = w.shape[0]
     first = batch.seq_first_row
     hc = h.to(self.compute)

@@ -40,8 +40,9 @@ def entries_batch(counts, starts, slots=None):
 
 # ------------------------------------------------------------------------------------------- kernels alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps,C", [(1, 40), (2, 300), (3, 64), (5, 257)])
-def test_short_conv_in_pieces(taps, C, dtype):
+@pytest.mark.parametrize("rows_per_thread", [0, 2, 8])
+@pytest.mark.parametrize("taps,C", [(1, 40), (2, 300), (3, 64), (4, 512), (5, 257)])
+def test_short_conv_in_pieces(taps, C, rows_per_thread, dtype):
     """Three sequences fed in three steps (many rows, a few, one each): every piece finds its past in the state."""
     g = torch.Generator().manual_seed(taps * 1000 + C)
     lens = [11, 2, 7]
@@ -58,7 +59,7 @@ def test_short_conv_in_pieces(taps, C, dtype):
         b = entries_batch(counts, pos, slots)
         h = torch.cat([hs[i][pos[i]:pos[i] + c] for i, c in enumerate(counts)]).to(DEV)
         out = torch.empty_like(h)
-        K().short_conv(h, w.t().contiguous().to(DEV), state if taps > 1 else None, b, out)
+        K().short_conv(h, w.t().contiguous().to(DEV), state if taps > 1 else None, b, out, rows_per_thread)
         r = 0
         for i, c in enumerate(counts):
             got[i].append(out[r:r + c].float().cpu()); r += c; pos[i] += c
