@@ -136,17 +136,26 @@ k_short_conv_rows(const TA* __restrict__ h, const float* __restrict__ w, const T
       }
     }
   const int r0 = blockIdx.x * CONV_ROWS, r1 = min(T, r0 + CONV_ROWS);
-  uint4 rows[CONV_ROWS];                                        // all of the chunk's inputs are requested at once
+  // Everything the chunk needs is requested at once, before anything is waited for: its rows, the rows before it
+  // (its first rows' past, if they belong to the same sequence), and the rows' places in their sequences.
+  uint4 rows[CONV_ROWS], halo[CONV_FEW_TAPS - 1];
+  int seqs[CONV_ROWS], ks[CONV_ROWS];
 #pragma unroll
   for (int r = 0; r < CONV_ROWS; r++)
     if (r0 + r < r1) rows[r] = *reinterpret_cast<const uint4*>(h + (size_t)(r0 + r) * C + c);
+#pragma unroll
+  for (int b = 1; b < CONV_FEW_TAPS; b++)
+    if (b < taps && r0 - b >= 0) halo[b - 1] = *reinterpret_cast<const uint4*>(h + (size_t)(r0 - b) * C + c);
+#pragma unroll
+  for (int r = 0; r < CONV_ROWS; r++) seqs[r] = r0 + r < r1 ? row_seq[r0 + r] : 0;
+#pragma unroll
+  for (int r = 0; r < CONV_ROWS; r++) ks[r] = r0 + r - seq_first_row[seqs[r]];
   int prev_seq = -1;
 #pragma unroll
   for (int r = 0; r < CONV_ROWS; r++) {
     const int row = r0 + r;
     if (row >= r1) break;
-    const int seq = row_seq[row];
-    const int k = row - seq_first_row[seq];
+    const int seq = seqs[r], k = ks[r];
     float cur[V];
     {
       const TA* e = reinterpret_cast<const TA*>(&rows[r]);
@@ -154,13 +163,15 @@ k_short_conv_rows(const TA* __restrict__ h, const float* __restrict__ w, const T
       for (int i = 0; i < V; i++) cur[i] = cima_to_f32<TA>(e[i]);
     }
     if (seq != prev_seq || k < taps - 1) {
-      // the past from scratch: rows of the step where they are the sequence's, its state before that
+      // the past from scratch: rows of the step where they are the sequence's (the chunk's first row has them
+      // at hand), its state before that
       const TA* st = state + (size_t)seq_slot[seq] * (taps - 1) * C + c;
 #pragma unroll
       for (int b = 1; b < CONV_FEW_TAPS; b++)
         if (b < taps) {
-          const TA* src = b <= k ? h + (size_t)(row - b) * C + c : st + (size_t)(taps - 1 - (b - k)) * C;
-          const uint4 raw = *reinterpret_cast<const uint4*>(src);
+          uint4 raw;
+          if (r == 0 && b <= k) raw = halo[b - 1];
+          else raw = *reinterpret_cast<const uint4*>(b <= k ? h + (size_t)(row - b) * C + c : st + (size_t)(taps - 1 - (b - k)) * C);
           const TA* e = reinterpret_cast<const TA*>(&raw);
 #pragma unroll
           for (int i = 0; i < V; i++) past[b - 1][i] = cima_to_f32<TA>(e[i]);
@@ -237,9 +248,11 @@ extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* s
   // 16-byte accesses: the rows of h, u and the state must all start on 16 bytes
   const int per16 = dtype == CIMA_F32 ? 4 : 8;
   const bool wide = C % per16 == 0 && (((uintptr_t)h | (uintptr_t)u | (uintptr_t)state | (uintptr_t)w) & 15) == 0;
-  // rows a thread walks: as many (8, 4, 2) as still leave every SM its full count of threads; else one (the kernel above)
+  // rows a thread walks: 8 where that still leaves the SMs a few hundred thousand threads; else one (the kernel above)
   const long long cells = (long long)T * (C / per16);
-  int rows_each = cells >= 8ll * 148 * 2048 ? 8 : (cells >= 4ll * 148 * 2048 ? 4 : (cells >= 2ll * 148 * 2048 ? 2 : 1));
+  // (measured inside a 2,048-row step at 3,584 channels: 8 rows a thread 14 to 16 us, one row 18 to 19, two rows 22; at
+  // 1,536 channels all variants 8 to 10)
+  int rows_each = cells >= 2ll * 148 * 2048 ? 8 : 1;
   if (rows_per_thread == 1 || rows_per_thread == 2 || rows_per_thread == 4 || rows_per_thread == 8) rows_each = rows_per_thread;
   else if (rows_per_thread != 0) return cima_fail(CIMA_E_ARG, "short_conv: %d rows a thread; 0 (chosen here), 1, 2, 4 or 8 are possible", rows_per_thread);
 #define RUN(TA) { \
