@@ -213,6 +213,8 @@ def test_attention_over_one_plane_decoding(dtype, R, heads):
     ("bfloat16", 128, 5, [260, 3], [65, 190]),             # sequences that go on
     ("bfloat16", 96, 3, [100, 64, 1], [0, 64, 7]),
     ("float32", 40, 2, [70, 5], [0, 130]),
+    ("bfloat16", 288, 2, [70, 5], [0, 130]),               # wider than any tiled kernel takes: the plain one, 9 values a lane
+    ("float32", 520, 1, [9, 3], [0, 66]),
 ])
 def test_attention_over_one_plane_many_rows(dtype, R, heads, counts, starts):
     g = torch.Generator().manual_seed(R * heads)
