@@ -121,14 +121,40 @@ template <typename TA> struct HlVec;
 template <> struct HlVec<float> { static constexpr int N = 4; };
 template <> struct HlVec<__nv_bfloat16> { static constexpr int N = 8; };
 
+// A decode step's latents can be appended by the same launch (both read the projection that ran just before): one
+// more row of blocks, of which the first does what k_latent_append does, warp m for row m.
+template <typename TA>
+struct LatentJob {
+  const TA* raw;                // null: no job
+  int ld;
+  const float* g;
+  float eps;
+  TA* cache;
+  CimaPaged pg;
+  const int *row_pos, *row_seq, *seq_slot;
+  int R;
+};
+
 template <typename TA>
 __global__ void __launch_bounds__(32 * HL_FEW_ROWS)
 k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __restrict__ out, int M, int N, int K, int lda, int ldo,
-                  int vec) {
+                  int vec, LatentJob<TA> job) {
   extern __shared__ __align__(16) float a_sh[];         // [M][Kp], Kp = K rounded up to 4
   const int Kp = (K + 3) & ~3;
   const int head = blockIdx.y;
   const int lane = threadIdx.x & 31, m = threadIdx.x >> 5;
+  if (job.raw && blockIdx.y == gridDim.y - 1) {
+    if (blockIdx.x != 0) return;
+    cima_pdl_wait();
+    const TA* r = job.raw + (size_t)m * job.ld;
+    float ss = 0.f;
+    for (int i = lane; i < job.R; i += 32) { const float v = cima_to_f32<TA>(r[i]); ss += v * v; }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)job.R + job.eps);
+    TA* dst = job.cache + job.pg.offset(job.seq_slot[job.row_seq[m]], job.row_pos[m], 0, 0);
+    for (int i = lane; i < job.R; i += 32) dst[i] = cima_from_f32<TA>(cima_to_f32<TA>(r[i]) * inv * job.g[i]);
+    return;
+  }
   const int n = blockIdx.x * 32 + lane;
   const bool live = n < N;
   const TA* wr = W + ((size_t)head * N + (live ? n : 0)) * K;
@@ -189,20 +215,50 @@ k_head_linear_few(const TA* __restrict__ A, const TA* __restrict__ W, TA* __rest
 }
 
 // a [M, heads, K] in rows of lda, w [heads, N, K] contiguous, out [M, heads, N] in rows of ldo; all of `dtype`.
+// raw (may be null) ... R: the arguments of cima_latent_append for the same M rows, done by the same launch; only for
+// the few rows of a decode step (M <= 8).
+static int head_linear_impl(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
+                            int ldo, const void* raw, int ld_raw, const float* g, float eps, void* cache, const int* table,
+                            int table_width, int ring, int page_size, const int* row_pos, const int* row_seq,
+                            const int* seq_slot, int R, cudaStream_t stream);
+
 extern "C" int cima_head_linear(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
                                 int ldo, cudaStream_t stream) {
+  return head_linear_impl(a, w, out, dtype, M, heads, N, K, lda, ldo, nullptr, 0, nullptr, 0.f, nullptr, nullptr, 0, 0, 0,
+                          nullptr, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int cima_head_linear_append(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
+                                       int ldo, const void* raw, int ld_raw, const float* g, float eps, void* cache,
+                                       const int* table, int table_width, int ring, int page_size, const int* row_pos,
+                                       const int* row_seq, const int* seq_slot, int R, cudaStream_t stream) {
+  if (M > HL_FEW_ROWS || (size_t)M * (K + 3) * 4 > 48 * 1024)
+    return cima_fail(CIMA_E_SIZE, "head_linear_append: %d rows of %d values; the launch that also appends takes at most %d rows", M, K, HL_FEW_ROWS);
+  if (!raw || !g || !cache || !table || R <= 0 || ld_raw < R)
+    return cima_fail(CIMA_E_ARG, "head_linear_append: the compressed rows (%d values in rows of %d), the norm's weight, the pages and their table are needed", R, ld_raw);
+  return head_linear_impl(a, w, out, dtype, M, heads, N, K, lda, ldo, raw, ld_raw, g, eps, cache, table, table_width, ring,
+                          page_size, row_pos, row_seq, seq_slot, R, stream);
+}
+
+static int head_linear_impl(const void* a, const void* w, void* out, int dtype, int M, int heads, int N, int K, int lda,
+                            int ldo, const void* raw, int ld_raw, const float* g, float eps, void* cache, const int* table,
+                            int table_width, int ring, int page_size, const int* row_pos, const int* row_seq,
+                            const int* seq_slot, int R, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (heads <= 0 || N <= 0 || K <= 0) return cima_fail(CIMA_E_SIZE, "head_linear: %d heads, N %d and K %d must be positive", heads, N, K);
   if (lda < heads * K || ldo < heads * N) return cima_fail(CIMA_E_SIZE, "head_linear: rows of (%d, %d) do not hold %d heads of (%d, %d)", lda, ldo, heads, K, N);
   if (heads > 65535 || (M + 63) / 64 > 65535) return cima_fail(CIMA_E_SIZE, "head_linear: %d heads / %d rows exceed one launch", heads, M);
   int rc;
   if (M <= HL_FEW_ROWS && (size_t)M * (K + 3) * 4 <= 48 * 1024) {
-    const dim3 grid((N + 31) / 32, heads);
+    const dim3 grid((N + 31) / 32, heads + (raw ? 1 : 0));
+    const CimaPaged pg{table, table_width, ring, page_size, 1, R, 1};
     const size_t smem = (size_t)M * ((K + 3) & ~3) * sizeof(float);
     const int esz = dtype == CIMA_F32 ? 4 : 2;
     const int vec = (((uintptr_t)w & 15) == 0 && ((size_t)K * esz) % 16 == 0) ? 1 : 0;      // every row of w starts on 16 bytes
-    if (dtype == CIMA_F32) rc = cima_launch(k_head_linear_few<float>, grid, dim3(32 * M), smem, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo, vec);
-    else if (dtype == CIMA_BF16) rc = cima_launch(k_head_linear_few<__nv_bfloat16>, grid, dim3(32 * M), smem, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo, vec);
+    if (dtype == CIMA_F32) rc = cima_launch(k_head_linear_few<float>, grid, dim3(32 * M), smem, stream, 1, (const float*)a, (const float*)w, (float*)out, M, N, K, lda, ldo, vec,
+                                                LatentJob<float>{(const float*)raw, ld_raw, g, eps, (float*)cache, pg, row_pos, row_seq, seq_slot, R});
+    else if (dtype == CIMA_BF16) rc = cima_launch(k_head_linear_few<__nv_bfloat16>, grid, dim3(32 * M), smem, stream, 1, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo, vec,
+                                                  LatentJob<__nv_bfloat16>{(const __nv_bfloat16*)raw, ld_raw, g, eps, (__nv_bfloat16*)cache, pg, row_pos, row_seq, seq_slot, R});
     else return cima_fail(CIMA_E_DTYPE, "head_linear: dtype code %d is neither float32 nor bfloat16", dtype);
   } else if (dtype == CIMA_BF16) {
     const dim3 grid((N + 63) / 64, (M + 63) / 64, heads);

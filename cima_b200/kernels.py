@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 23
+ABI_VERSION = 24
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -77,6 +77,8 @@ _SIGNATURES = {
     "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp],
     "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_head_linear_append": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp,
+                                _i, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
@@ -668,9 +670,16 @@ class Kernels:
                                                 kv.ring_pages, kv.page_size, batch.row_pos.data_ptr(), batch.row_seq.data_ptr(),
                                                 batch.seq_slot.data_ptr(), T, R, self._stream()), "latent_append")
 
-    def head_linear(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    FUSED_APPEND_ROWS = 8       # a step of at most this many rows appends its latents in the launch of its first head product
+
+    def head_linear(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, append=None) -> None:
         """out[t, h, :] = a[t, h, :] @ w[h].T for every head: a [T, heads * K] (rows may be slices of a wider
-        matrix), w [heads, N, K], out [T, heads * N]; one dtype."""
+        matrix), w [heads, N, K], out [T, heads * N]; one dtype.  ``append = (raw, g, eps, kv, batch)``: the arguments
+        of ``latent_append`` for the same rows, done by the same launch (a decode step's few rows) or, for more rows,
+        by a launch of its own first."""
+        if append is not None and (a.shape[0] > self.FUSED_APPEND_ROWS or a.shape[0] * (w.shape[2] + 3) * 4 > 48 * 1024):
+            self.latent_append(*append)
+            append = None
         self._need(w, "w", a.dtype, 3); self._need(out, "out", a.dtype, 2)
         heads, N, K = w.shape
         T = a.shape[0]
@@ -681,6 +690,20 @@ class Kernels:
             # many bfloat16 rows: the library's batched product, as for the other products of more than 8 rows
             self.library_launches += 1
             torch.bmm(a.view(T, heads, K).transpose(0, 1), w.transpose(1, 2), out=out.view(T, heads, N).transpose(0, 1))
+            return
+        if append is not None:
+            raw, g, eps, kv, batch = append
+            self._need(g, "g", torch.float32, 1); self._need(kv.storage, "cache", raw.dtype, 5)
+            R = raw.shape[1]
+            if (raw.dtype is not a.dtype or raw.shape[0] != T or raw.stride(1) != 1 or g.numel() != R
+                    or tuple(kv.storage.shape[1:]) != (1, 1, kv.page_size, R)):
+                raise KernelError(f"head_linear: the latents to append, raw {tuple(raw.shape)}, g {tuple(g.shape)}, pages "
+                                  f"{tuple(kv.storage.shape)}, do not agree with {T} rows")
+            self._check(self.lib.cima_head_linear_append(
+                a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K, a.stride(0), out.stride(0),
+                raw.data_ptr(), raw.stride(0), g.data_ptr(), eps, kv.storage.data_ptr(), kv.block_table.data_ptr(),
+                kv.block_table.shape[1], kv.ring_pages, kv.page_size, batch.row_pos.data_ptr(), batch.row_seq.data_ptr(),
+                batch.seq_slot.data_ptr(), R, self._stream()), "head_linear_append")
             return
         self._check(self.lib.cima_head_linear(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K,
                                               a.stride(0), out.stride(0), self._stream()), "head_linear")

@@ -121,10 +121,11 @@ class LatentAttention:
         rows = u.shape[0]
         kv = cache.layer_kv(site)
         ql = self.q_latent.store(u)                                  # [rows, heads * head_dim (+ kv_rank)]
-        if self.own:
-            K_.latent_append(ql[:, self.qd:], self.latent_norm, self.latent_eps, kv, batch)
         qa = rt.empty(rows, self.heads * self.rank)
-        K_.head_linear(ql[:, :self.qd], self.k_up_t, qa)
+        # (the step's latents go into the pages before the attention reads them: in the same launch for the few rows
+        # of a decode step, in one of their own before it otherwise)
+        K_.head_linear(ql[:, :self.qd], self.k_up_t, qa,
+                       append=(ql[:, self.qd:], self.latent_norm, self.latent_eps, kv, batch) if self.own else None)
         ol = rt.empty(rows, self.heads * self.rank)
         K_.attention(qa, kv, batch, ol, self.heads, 1, self.rank, self.spec.scale, 0, True)
         att = rt.empty(rows, self.od)

@@ -259,7 +259,9 @@ def _latent_append(self, raw, g, eps, kv, batch):
         kv.storage[page, 0, 0, off, :] = c[t].to(kv.storage.dtype)
 
 
-def _head_linear(self, a, w, out):
+def _head_linear(self, a, w, out, append=None):
+    if append is not None:
+        self.latent_append(*append)
     heads, N, K = w.shape
     y = torch.einsum("thk,hnk->thn", a.reshape(a.shape[0], heads, K).to(self.compute), w.to(self.compute))
     out.copy_(y.reshape(a.shape[0], heads * N).to(out.dtype))

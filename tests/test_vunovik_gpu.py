@@ -153,6 +153,37 @@ def test_head_linear(T, heads, N, K_, dtype):
     assert (out.cpu().double() - want).abs().max().item() < (2e-5 if dtype == "float32" else 3e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,R", [(1, 24), (5, 64), (8, 200), (12, 32)])
+def test_head_linear_appends_the_latents_of_a_decode_step(rows, R, dtype):
+    """The first head product of a decode step writes the step's latents in its own launch (more rows: in one before
+    it): the pages and the product are what the two kernels give apart."""
+    g = torch.Generator().manual_seed(rows + R)
+    heads, N, K_ = 3, 40, 16
+    wide = torch.randn(rows, heads * K_ + R, generator=g).to(DT[dtype]).to(DEV)          # q heads | compressed vector
+    w = (torch.randn(heads, N, K_, generator=g) / 4).to(DT[dtype]).to(DEV)
+    gw = (1 + 0.1 * torch.randn(R, generator=g)).to(DEV)
+    pages, outs = [], []
+    for fused in (False, True):
+        cache = latent_cache(R, dtype, n_pages=rows + 3, slots=rows)
+        slots = cache.open(rows)
+        starts = [(7 * i) % 70 for i in range(rows)]
+        for s_, n in zip(slots, starts):
+            cache.reserve(s_, n + 1)
+        cache.flush()
+        kv = cache.layer_kv(0)
+        b = entries_batch([1] * rows, starts, slots)
+        out = torch.empty(rows, heads * N, dtype=DT[dtype], device=DEV)
+        if fused:
+            K().head_linear(wide[:, :heads * K_], w, out, append=(wide[:, heads * K_:], gw, 1e-5, kv, b))
+        else:
+            K().latent_append(wide[:, heads * K_:], gw, 1e-5, kv, b)
+            K().head_linear(wide[:, :heads * K_], w, out)
+        pages.append(kv.storage.float().cpu()); outs.append(out.float().cpu())
+    assert torch.equal(outs[0], outs[1])
+    assert pages[0].abs().sum() > 0 and (pages[0] - pages[1]).abs().max().item() < (1e-6 if dtype == "float32" else 2e-2)
+
+
 def fill_latents(cache, slots, lens, R, dtype, g):
     """Random latents for ``lens`` positions of each slot, written through the block table; returns them."""
     kv = cache.layer_kv(0)
