@@ -14,7 +14,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Union
 
-from .config import (ArchitectureEntry, ConfigError, Qwen2Config, VunovikConfig, lookup_architecture, read_config_json,
+from .config import (ArchitectureEntry, ConfigError, GisiraxConfig, Qwen2Config, VunovikConfig, lookup_architecture, read_config_json,
                      register_architecture, registered_architectures)
 from .sampling import GenOptions, OptionError
 
@@ -22,6 +22,9 @@ register_architecture(ArchitectureEntry(name=Qwen2Config.ARCHITECTURE, model_typ
                                         parse=Qwen2Config.from_dict, spec=Qwen2Config.model_spec))
 register_architecture(ArchitectureEntry(name=VunovikConfig.ARCHITECTURE, model_type="vunovik",
                                         parse=VunovikConfig.from_dict, spec=VunovikConfig.model_spec))
+register_architecture(ArchitectureEntry(name=GisiraxConfig.ARCHITECTURE, model_type="gisirax",
+                                        parse=GisiraxConfig.from_dict, spec=GisiraxConfig.model_spec,
+                                        parse_with_shapes=GisiraxConfig.from_dict))
 
 __version__ = "0.1.0"
 
@@ -137,5 +140,5 @@ def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int 
 
 
 __all__ = ["LM", "load", "write_random_model", "eos_ids_of", "GenOptions", "OptionError", "ConfigError",
-           "Qwen2Config", "VunovikConfig", "register_architecture", "registered_architectures", "lookup_architecture",
+           "Qwen2Config", "VunovikConfig", "GisiraxConfig", "register_architecture", "registered_architectures", "lookup_architecture",
            "read_config_json", "ArchitectureEntry"]

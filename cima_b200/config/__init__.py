@@ -1,10 +1,11 @@
-from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec, ShortConvSpec)
+from .specs import (BigramSpec, BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec, ShortConvSpec)
 from .registry import (ArchitectureEntry, UnknownArchitecture, lookup_architecture,
                        read_config_json, register_architecture, registered_architectures)
 from .qwen2 import ConfigError, Qwen2Config
 from .vunovik import VunovikConfig
+from .gisirax import GisiraxConfig
 from . import shapes
 
 __all__ = ["BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec",
            "ArchitectureEntry", "UnknownArchitecture", "lookup_architecture", "read_config_json",
-           "register_architecture", "registered_architectures", "ConfigError", "Qwen2Config", "VunovikConfig", "ShortConvSpec"]
+           "register_architecture", "registered_architectures", "ConfigError", "Qwen2Config", "VunovikConfig", "GisiraxConfig", "ShortConvSpec", "BigramSpec"]

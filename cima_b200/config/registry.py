@@ -22,6 +22,9 @@ class ArchitectureEntry:
     model_type: str                             # e.g. "qwen2"
     parse: Callable[[Dict[str, Any]], Any]      # config.json dict -> typed configuration
     spec: Callable[[Any], ModelSpec]            # typed configuration -> ModelSpec
+    # config.json dict, {tensor name: shape} of the model folder -> typed configuration, for a design in which some
+    # sizes stand in no key of config.json and are read off the stored tensors; None: ``parse`` alone serves
+    parse_with_shapes: Any = None
 
 
 _BY_NAME: Dict[str, ArchitectureEntry] = {}

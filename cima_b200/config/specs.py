@@ -18,7 +18,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str                    # "rmsnorm"
+    kind: str                    # "rmsnorm" | "dyt" (tanh(alpha x) * w + b: no row statistics, eps unused)
     size: int
     eps: float
     params: Dict[str, Any] = field(default_factory=dict)
@@ -30,6 +30,7 @@ class PositionSpec:
     head_dim: int
     rotary_dim: int              # how many leading dims of a head rotate (<= head_dim, even)
     theta: float
+    # "scaling": {"factor", "low", "high", "original"}: frequencies rescaled by their wavelength (see parts/position.py)
     params: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -72,9 +73,21 @@ class ShortConvSpec:
 
 
 @dataclass(frozen=True)
+class BigramSpec:
+    """A second embedding table beside the token table, addressed by a hash of the token and the one before it:
+    row (prev * mul_prev + tok * mul_cur) mod buckets, and row ``buckets`` (the table's last) for a sequence's first
+    token.  The token before a step's first row travels with the sequence as state."""
+    name: str
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     kind: str                    # "prenorm": x += mixer(norm(x)); x += ffn(norm(x))
                                  # "parallel": h = norm(x); x += mixer(conv(h)) + ffn(h)
+                                 # "sandwich": x += m * post(mixer(norm(x))); x += m * post(ffn(norm(x)))
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]      # None: the layer has no feed-forward ("parallel" only)
     mixer_norm: NormSpec
@@ -85,6 +98,11 @@ class BlockSpec:
     names: Dict[str, str] = field(default_factory=dict)
     # a short convolution in front of the mixer (its weight's stem is names["mixer_conv"]); None = none
     mixer_conv: Optional[ShortConvSpec] = None
+    # "sandwich": the norms behind the sublayers (stems names["mixer_post_norm"], names["ffn_post_norm"]) and the
+    # factor of what a sublayer adds to the stream
+    mixer_post_norm: Optional[NormSpec] = None
+    ffn_post_norm: Optional[NormSpec] = None
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -103,6 +121,7 @@ class ModelSpec:
     final_norm_name: str
     head_name: str
     embed_scale: float = 1.0
+    embed_bigram: Optional[BigramSpec] = None       # a hashed bigram table added to the token embedding
     # A checkpoint of an untied model that stores no head tensor: the table serves as the head
     # (the reference decides so, src/models/transformer.rs:810, and warns, :839-841).
     head_may_be_absent: bool = False

@@ -14,7 +14,7 @@ __global__ void __launch_bounds__(128)
 k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cache, CimaPaged pg,
                   const int* __restrict__ row_pos, const int* __restrict__ row_seq,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
-                  TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window) {
+                  TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window, float sink) {
   cima_pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -66,6 +66,7 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
     m = m2;
   }
   TA* op = out + (size_t)row * ldo + (size_t)h * hd;
+  l += sink * expf(-m);                 // `sink` entries of score 0 that carry no value (0: an ordinary softmax)
   const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < NI; i++) {
@@ -79,7 +80,7 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
                                     int table_width, int ring, int page_size, const int* row_pos,
                                     const int* row_seq, const int* seq_slot, const int* seq_first_row, void* out,
                                     int ldo, int T, int nh, int nkv, int hd, float scale, int window,
-                                    int from_cache, int planes, cudaStream_t stream) {
+                                    int from_cache, int planes, float sink, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd > 1024) return cima_fail(CIMA_E_SIZE, "attention_plain: head_dim %d is outside 1..1024", hd);
   if (planes != 1 && planes != 2) return cima_fail(CIMA_E_ARG, "attention_plain: %d planes; pages hold keys | values (2) or one shared vector (1)", planes);
@@ -90,7 +91,7 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
   dim3 grid((T + 3) / 4, nh);
 #define LAUNCH(TA, FC) { int rc_ = hd <= 256 ? LAUNCH_NI(TA, FC, 8) : LAUNCH_NI(TA, FC, 32); if (rc_) return rc_; }
 #define LAUNCH_NI(TA, FC, NI) cima_launch(k_attention_plain<TA, FC, NI>, dim3(grid), dim3(128), (size_t)(0), stream, 1, (const TA*)qkv, ld, (const TA*)cache, pg, \
-    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window)
+    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window, sink)
   if (dtype == CIMA_F32) { if (from_cache) LAUNCH(float, true) else LAUNCH(float, false) }
   else if (dtype == CIMA_BF16) { if (from_cache) LAUNCH(__nv_bfloat16, true) else LAUNCH(__nv_bfloat16, false) }
   else return cima_fail(CIMA_E_DTYPE, "attention_plain: dtype code %d is neither float32 nor bfloat16", dtype);

@@ -1,0 +1,81 @@
+// Two small norms behind the recurrent mixers, float32 throughout, one rounding at the store:
+//   group_rmsnorm_gate   out = o / sqrt(mean_group(o^2) + eps) * w * sigmoid(gate)      per group of n values of a row
+//                        (a group = a head's values with one shared weight [n], or the whole row with a weight [G n])
+//   rms_mean             x += (1 / B) * sum_b  y_b / sqrt(mean(y_b^2) + eps) * w_b        B <= 4 branches of one width
+#include "common.cuh"
+
+namespace {
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(128)
+k_group_rmsnorm_gate(const float* __restrict__ o, const float* __restrict__ w, const TG* __restrict__ gate, int ldg,
+                     TO* __restrict__ out, long long units, int groups, int n, int shared_w, float eps) {
+  cima_pdl_wait();
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= units) return;
+  const int lane = threadIdx.x & 31;
+  const long long row = unit / groups;
+  const int grp = (int)(unit - row * groups);
+  const float* src = o + ((size_t)row * groups + grp) * n;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) ss = fmaf(src[i], src[i], ss);
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float r = 1.0f / sqrtf(ss / (float)n + eps);
+  const float* wp = w + (shared_w ? 0 : (size_t)grp * n);
+  const TG* gp = gate ? gate + (size_t)row * ldg + (size_t)grp * n : nullptr;
+  TO* dst = out + ((size_t)row * groups + grp) * n;
+  for (int i = lane; i < n; i += 32) {
+    float y = src[i] * r * wp[i];
+    if (gp) y *= 1.0f / (1.0f + expf(-cima_to_f32<TG>(gp[i])));
+    dst[i] = cima_from_f32<TO>(y);
+  }
+}
+
+struct Branches { const float* y[4]; const float* w[4]; int n; };
+
+__global__ void __launch_bounds__(256)
+k_rms_mean(Branches br, float* __restrict__ x, int H, float eps) {
+  cima_pdl_wait();
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  float r[4];
+  for (int b = 0; b < br.n; b++) {
+    const float* y = br.y[b] + row * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) ss = fmaf(y[c], y[c], ss);
+    ss = cima_block_sum(ss, red);
+    r[b] = 1.0f / sqrtf(ss / (float)H + eps);
+  }
+  const float inv = 1.0f / (float)br.n;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float s = 0.f;
+    for (int b = 0; b < br.n; b++) s += br.y[b][row * H + c] * r[b] * br.w[b][c];
+    x[row * H + c] += s * inv;
+  }
+}
+}  // namespace
+
+// o [T, groups * n] float32; w [n] (shared_w) or [groups * n]; gate [T, ldg] (gdtype) or null; out [T, groups * n] (odtype).
+extern "C" int cima_group_rmsnorm_gate(const float* o, const float* w, const void* gate, int ldg, void* out, int dtype, int T,
+                                       int groups, int n, int shared_w, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (groups <= 0 || n <= 0) return cima_fail(CIMA_E_SIZE, "group_rmsnorm_gate: %d groups of %d values must be positive", groups, n);
+  const long long units = (long long)T * groups;
+  const dim3 grid((unsigned)((units + 3) / 4));
+  int rc;
+  if (dtype == CIMA_F32) rc = cima_launch(k_group_rmsnorm_gate<float, float>, grid, dim3(128), (size_t)0, stream, 1, o, w, (const float*)gate, ldg, (float*)out, units, groups, n, shared_w, eps);
+  else if (dtype == CIMA_BF16) rc = cima_launch(k_group_rmsnorm_gate<__nv_bfloat16, __nv_bfloat16>, grid, dim3(128), (size_t)0, stream, 1, o, w, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, units, groups, n, shared_w, eps);
+  else return cima_fail(CIMA_E_DTYPE, "group_rmsnorm_gate: dtype code %d is neither float32 nor bfloat16", dtype);
+  return rc ? rc : cima_launch_result();
+}
+
+// ys / ws: n_branches pointers to float32 [T, H] and [H]; x [T, H] float32 is added to.
+extern "C" int cima_rms_mean(const float* const* ys, const float* const* ws, int n_branches, float* x, int T, int H, float eps,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_branches < 1 || n_branches > 4 || H <= 0) return cima_fail(CIMA_E_SIZE, "rms_mean: %d branches (1..4) of width %d", n_branches, H);
+  Branches br{};
+  br.n = n_branches;
+  for (int b = 0; b < n_branches; b++) { br.y[b] = ys[b]; br.w[b] = ws[b]; }
+  int rc = cima_launch(k_rms_mean, dim3(T), dim3(256), (size_t)0, stream, 1, br, x, H, eps);
+  return rc ? rc : cima_launch_result();
+}

@@ -1,0 +1,231 @@
+// A routed feed-forward (mixture of experts) in five launches, none of which needs a number on the host:
+//   moe_route     scores s = sigmoid(logits); groups of neighbouring experts scored by their two best; the best `keep`
+//                 groups stay; the `top` best experts among them; weights s / (sum s + 1e-20) * scale        (float32)
+//   moe_sort      the (row, choice) pairs ordered by expert: offsets of every expert's pairs and of its row tiles
+//   moe_gemm 0    z[i] = act(W_gate[e] h[row]) * (W_up[e] h[row])      for the sorted pairs i (a tile = 32 pairs of one expert)
+//   moe_gemm 1    y[pair] = W_down[e] z[i]                             float32, back at the pair's own place
+//   moe_combine   x[row] += sum_j weight[row, j] * y[row * top + j]    ascending j, float32
+// A pair's sums run over k in ascending order with one accumulator, so its result does not depend on which other
+// rows share its tile, nor on the order in which the sort placed the pairs of an expert.
+#include "common.cuh"
+
+namespace {
+constexpr int MOE_MAX_EXPERTS = 1024;
+constexpr int BM = 32, BN = 64, BK = 16;
+
+__global__ void __launch_bounds__(128)
+k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int keep, float scale, int* __restrict__ idx,
+            float* __restrict__ wgt) {
+  cima_pdl_wait();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= T) return;
+  float* s = scores + (size_t)row * E;
+  for (int e = 0; e < E; e++) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  const int per = E / groups;
+  unsigned long long kept = ~0ull;
+  if (keep < groups) {
+    kept = 0ull;
+    for (int c = 0; c < keep; c++) {
+      int best = -1;
+      float bs = -1.f;
+      for (int gi = 0; gi < groups; gi++) {
+        if ((kept >> gi) & 1ull) continue;
+        float a1 = -1.f, a2 = -1.f;                        // the group's two largest scores
+        for (int e = gi * per; e < (gi + 1) * per; e++) {
+          const float v = s[e];
+          if (v > a1) { a2 = a1; a1 = v; } else if (v > a2) a2 = v;
+        }
+        const float sc = per >= 2 ? a1 + a2 : a1;
+        if (sc > bs) { bs = sc; best = gi; }
+      }
+      kept |= 1ull << best;
+    }
+  }
+  float sum = 0.f;
+  for (int c = 0; c < top; c++) {
+    int best = -1;
+    float bs = -1.f;
+    for (int e = 0; e < E; e++) {
+      if (!((kept >> (e / per)) & 1ull)) continue;
+      if (s[e] > bs) { bs = s[e]; best = e; }
+    }
+    idx[(size_t)row * top + c] = best;
+    wgt[(size_t)row * top + c] = bs;
+    sum += bs;
+    s[best] = -2.f;                                        // taken
+  }
+  const float f = scale / (sum + 1e-20f);
+  for (int c = 0; c < top; c++) wgt[(size_t)row * top + c] *= f;
+}
+
+// offsets [E + 1]: first sorted pair of every expert; tiles [E + 1]: first row tile of every expert; perm [P]: the
+// pair at every sorted place.  One block.
+__global__ void __launch_bounds__(1024)
+k_moe_sort(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ perm) {
+  cima_pdl_wait();
+  __shared__ int cnt[MOE_MAX_EXPERTS];
+  __shared__ int off[MOE_MAX_EXPERTS + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, t = 0;
+    for (int e = 0; e < E; e++) {
+      off[e] = o; offsets[e] = o; tiles[e] = t;
+      o += cnt[e];
+      t += (cnt[e] + BM - 1) / BM;
+    }
+    off[E] = o; offsets[E] = o; tiles[E] = t;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = idx[p];
+    perm[off[e] + atomicAdd(&cnt[e], 1)] = p;
+  }
+}
+
+// MODE 0: A = h [T, K] gathered by row = perm[i] / top; W = [E, 2 N, K] (gate rows, then up rows); out z [P, N] (TA) at i.
+// MODE 1: A = z [P, K] at i; W = [E, N, K]; out y [P, N] float32 at perm[i].
+template <typename TA, typename TW, int MODE>
+__global__ void __launch_bounds__(256)
+k_moe_gemm(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __restrict__ out, const int* __restrict__ offsets,
+           const int* __restrict__ tiles, const int* __restrict__ perm, int E, int top, int N, int K, int act) {
+  cima_pdl_wait();
+  __shared__ float As[BK][BM + 1];
+  __shared__ float Bs[MODE == 0 ? 2 : 1][BK][BN + 1];
+  __shared__ int s_row[BM];
+  __shared__ int s_e, s_i0, s_n;
+  if (threadIdx.x == 0) {
+    const int tile = blockIdx.x;
+    int e = -1;
+    if (tile < tiles[E]) {
+      // the expert whose tiles hold this one (tiles is ascending; experts without pairs own none)
+      int lo = 0, hi = E - 1;
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (tiles[mid] <= tile) lo = mid; else hi = mid - 1; }
+      e = lo;
+      while (tiles[e + 1] <= tile) e++;                     // (skips experts without tiles that share the start)
+      s_i0 = offsets[e] + (tile - tiles[e]) * BM;
+      s_n = min(BM, offsets[e + 1] - s_i0);
+    }
+    s_e = e;
+  }
+  __syncthreads();
+  const int e = s_e;
+  if (e < 0) return;
+  const int i0 = s_i0, nrows = s_n;
+  if (threadIdx.x < BM) {
+    const int r = threadIdx.x;
+    s_row[r] = r < nrows ? (MODE == 0 ? perm[i0 + r] / top : i0 + r) : -1;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.y * BN;
+  const TW* Wg = W + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // tx: 4 columns each, ty: 2 rows each
+  float acc[2][4] = {}, acc2[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int t = threadIdx.x; t < BM * BK; t += 256) {
+      const int r = t / BK, kk = t - r * BK;
+      const int src = s_row[r];
+      As[kk][r] = (src >= 0 && k0 + kk < K) ? cima_to_f32<TA>(A[(size_t)src * lda + k0 + kk]) : 0.f;
+    }
+    for (int t = threadIdx.x; t < BN * BK; t += 256) {
+      const int c = t / BK, kk = t - c * BK;
+      const bool ok = n0 + c < N && k0 + kk < K;
+      Bs[0][kk][c] = ok ? cima_to_f32<TW>(Wg[(size_t)(n0 + c) * K + k0 + kk]) : 0.f;
+      if (MODE == 0) Bs[1][kk][c] = ok ? cima_to_f32<TW>(Wg[(size_t)(N + n0 + c) * K + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float b = Bs[0][kk][tx * 4 + j];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+        if (MODE == 0) {
+          const float b2 = Bs[1][kk][tx * 4 + j];
+          acc2[0][j] = fmaf(a0, b2, acc2[0][j]);
+          acc2[1][j] = fmaf(a1, b2, acc2[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const int r = ty * 2 + i;
+    if (r >= nrows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int c = n0 + tx * 4 + j;
+      if (c >= N) continue;
+      if (MODE == 0) {
+        // the gate is rounded to the activations' dtype before its activation, as a stored projection would be
+        const float gt = cima_to_f32<TA>(cima_from_f32<TA>(acc[i][j])), up = cima_to_f32<TA>(cima_from_f32<TA>(acc2[i][j]));
+        reinterpret_cast<TA*>(out)[(size_t)(i0 + r) * N + c] = cima_from_f32<TA>(cima_gate_act(gt, act) * up);
+      } else {
+        reinterpret_cast<float*>(out)[(size_t)perm[i0 + r] * N + c] = acc[i][j];
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, float* __restrict__ x, int top, int H) {
+  cima_pdl_wait();
+  const size_t row = blockIdx.x;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float s = 0.f;
+    for (int j = 0; j < top; j++) s = fmaf(wgt[row * top + j], y[(row * top + j) * H + c], s);
+    x[row * H + c] += s;
+  }
+}
+}  // namespace
+
+// scores [T, E] float32: the router's logits on entry, scratch afterwards.  idx [T, top] int32, wgt [T, top] float32.
+extern "C" int cima_moe_route(float* scores, int T, int E, int top, int groups, int keep, float scale, int* idx, float* wgt,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || groups > 64 || E % groups || keep <= 0 || keep > groups)
+    return cima_fail(CIMA_E_SIZE, "moe_route: %d experts in %d groups of which %d stay are not accepted (at most %d experts in at most 64 equal groups)", E, groups, keep, MOE_MAX_EXPERTS);
+  if (top <= 0 || top > keep * (E / groups)) return cima_fail(CIMA_E_SIZE, "moe_route: %d choices among %d experts that stay", top, keep * (E / groups));
+  int rc = cima_launch(k_moe_route, dim3((T + 127) / 128), dim3(128), (size_t)0, stream, 1, scores, T, E, top, groups, keep, scale, idx, wgt);
+  return rc ? rc : cima_launch_result();
+}
+
+extern "C" int cima_moe_sort(const int* idx, int P, int E, int* offsets, int* tiles, int* perm, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_EXPERTS) return cima_fail(CIMA_E_SIZE, "moe_sort: %d experts (at most %d)", E, MOE_MAX_EXPERTS);
+  int rc = cima_launch(k_moe_sort, dim3(1), dim3(1024), (size_t)0, stream, 1, idx, P, E, offsets, tiles, perm);
+  return rc ? rc : cima_launch_result();
+}
+
+// mode 0: a [T, lda] (adtype), w [E, 2 N, K] (wdtype), out [P, N] (adtype); mode 1: a [P, lda], w [E, N, K], out [P, N] float32.
+extern "C" int cima_moe_gemm(const void* a, int adtype, int lda, const void* w, int wdtype, void* out, const int* offsets,
+                             const int* tiles, const int* perm, int P, int E, int top, int N, int K, int mode, int act,
+                             cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (N <= 0 || K <= 0 || E <= 0 || top <= 0) return cima_fail(CIMA_E_SIZE, "moe_gemm: sizes must be positive");
+  if (mode != 0 && mode != 1) return cima_fail(CIMA_E_ARG, "moe_gemm: mode %d is neither 0 (gate | up) nor 1 (down)", mode);
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "moe_gemm: activation code %d is unknown", act);
+  const dim3 grid((unsigned)((P + BM - 1) / BM + E), (unsigned)((N + BN - 1) / BN));
+  if (grid.y > 65535) return cima_fail(CIMA_E_SIZE, "moe_gemm: %d outputs exceed one launch", N);
+  int rc;
+#define RUN(TA, TW, M) rc = cima_launch(k_moe_gemm<TA, TW, M>, grid, dim3(256), (size_t)0, stream, 1, (const TA*)a, lda, (const TW*)w, out, offsets, tiles, perm, E, top, N, K, act)
+  if (adtype == CIMA_F32 && wdtype == CIMA_F32) { if (mode == 0) RUN(float, float, 0); else RUN(float, float, 1); }
+  else if (adtype == CIMA_BF16 && wdtype == CIMA_BF16) { if (mode == 0) RUN(__nv_bfloat16, __nv_bfloat16, 0); else RUN(__nv_bfloat16, __nv_bfloat16, 1); }
+  else if (adtype == CIMA_BF16 && wdtype == CIMA_F32) { if (mode == 0) RUN(__nv_bfloat16, float, 0); else RUN(__nv_bfloat16, float, 1); }
+  else return cima_fail(CIMA_E_DTYPE, "moe_gemm: activations of dtype %d with weights of dtype %d are not accepted", adtype, wdtype);
+#undef RUN
+  return rc ? rc : cima_launch_result();
+}
+
+extern "C" int cima_moe_combine(const float* y, const float* wgt, float* x, int T, int top, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, x, top, H);
+  return rc ? rc : cima_launch_result();
+}

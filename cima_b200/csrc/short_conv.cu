@@ -19,7 +19,7 @@ template <typename TA, bool ONE_ROW>
 __global__ void __launch_bounds__(CONV_THREADS)
 k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restrict__ state,
              const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
-             TA* __restrict__ u, int C, int taps) {
+             TA* __restrict__ u, int C, int taps, int add_input, int act) {
   cima_pdl_wait();
   const int row = blockIdx.x;
   const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
@@ -29,7 +29,7 @@ k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restri
   const int slot = seq_slot[seq];
   TA* st = state + (size_t)slot * (taps - 1) * C + c;
   const float cur = cima_to_f32<TA>(h[(size_t)row * C + c]);
-  float acc = cur;
+  float acc = add_input ? cur : 0.f;
   float old[CONV_MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < CONV_MAX_TAPS; j++) {
@@ -42,6 +42,7 @@ k_short_conv(const TA* __restrict__ h, const float* __restrict__ w, TA* __restri
     old[j] = v;
     acc = fmaf(w[(size_t)j * C + c], v, acc);
   }
+  if (act >= 0) acc = cima_gate_act(acc, act);
   u[(size_t)row * C + c] = cima_from_f32<TA>(acc);
   if (ONE_ROW) {
     // the state moves on by one position: entries 1 .. taps - 2 go down, the row's input comes last
@@ -64,7 +65,7 @@ template <typename TA>
 __global__ void __launch_bounds__(CONV_THREADS)
 k_short_conv_wide(const TA* __restrict__ h, const float* __restrict__ w, const TA* __restrict__ state,
                   const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
-                  TA* __restrict__ u, int C, int taps) {
+                  TA* __restrict__ u, int C, int taps, int add_input, int act) {
   cima_pdl_wait();
   constexpr int V = ConvVec<TA>::N;
   const int row = blockIdx.x;
@@ -78,7 +79,7 @@ k_short_conv_wide(const TA* __restrict__ h, const float* __restrict__ w, const T
     const uint4 raw = *reinterpret_cast<const uint4*>(h + (size_t)row * C + c);
     const TA* e = reinterpret_cast<const TA*>(&raw);
 #pragma unroll
-    for (int i = 0; i < V; i++) acc[i] = cur[i] = cima_to_f32<TA>(e[i]);
+    for (int i = 0; i < V; i++) { cur[i] = cima_to_f32<TA>(e[i]); acc[i] = add_input ? cur[i] : 0.f; }
   }
   for (int j = 0; j < taps; j++) {
     const int back = taps - 1 - j;
@@ -105,7 +106,7 @@ k_short_conv_wide(const TA* __restrict__ h, const float* __restrict__ w, const T
   uint4 outv;
   TA* o = reinterpret_cast<TA*>(&outv);
 #pragma unroll
-  for (int i = 0; i < V; i++) o[i] = cima_from_f32<TA>(acc[i]);
+  for (int i = 0; i < V; i++) o[i] = cima_from_f32<TA>(act >= 0 ? cima_gate_act(acc[i], act) : acc[i]);
   *reinterpret_cast<uint4*>(u + (size_t)row * C + c) = outv;
 }
 
@@ -120,7 +121,7 @@ template <typename TA, int CONV_ROWS>
 __global__ void __launch_bounds__(CONV_THREADS)
 k_short_conv_rows(const TA* __restrict__ h, const float* __restrict__ w, const TA* __restrict__ state,
                   const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
-                  TA* __restrict__ u, int T, int C, int taps) {
+                  TA* __restrict__ u, int T, int C, int taps, int add_input, int act) {
   cima_pdl_wait();
   constexpr int V = ConvVec<TA>::N;
   const int c = (blockIdx.y * CONV_THREADS + threadIdx.x) * V;
@@ -180,7 +181,7 @@ k_short_conv_rows(const TA* __restrict__ h, const float* __restrict__ w, const T
     }
     float acc[V];
 #pragma unroll
-    for (int i = 0; i < V; i++) acc[i] = cur[i];
+    for (int i = 0; i < V; i++) acc[i] = add_input ? cur[i] : 0.f;
 #pragma unroll
     for (int j = 0; j < CONV_FEW_TAPS; j++)
       if (j < taps) {
@@ -197,7 +198,7 @@ k_short_conv_rows(const TA* __restrict__ h, const float* __restrict__ w, const T
     uint4 outv;
     TA* o = reinterpret_cast<TA*>(&outv);
 #pragma unroll
-    for (int i = 0; i < V; i++) o[i] = cima_from_f32<TA>(acc[i]);
+    for (int i = 0; i < V; i++) o[i] = cima_from_f32<TA>(act >= 0 ? cima_gate_act(acc[i], act) : acc[i]);
     *reinterpret_cast<uint4*>(u + (size_t)row * C + c) = outv;
     // this row becomes the next one's nearest past
 #pragma unroll
@@ -233,12 +234,14 @@ k_short_conv_state(const TA* __restrict__ h, TA* __restrict__ state, const int* 
   }
 }
 
+// add_input 0 leaves the input out of the sum (a plain convolution); act >= 0 applies that activation (CIMA_ACT_*) to the sum.
 // h, u [T, C] and state [slots, taps - 1, C] of one dtype; w [taps, C] float32.  one_row != 0: row r is sequence r's only row.
 // rows_per_thread: 0, or how many consecutive rows a thread of the many-row kernel walks (the result does not depend on it).
 extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* state, const int* row_seq, const int* seq_slot,
                                const int* seq_first_row, void* u, int T, int n_seqs, int C, int taps, int one_row,
-                               int rows_per_thread, cudaStream_t stream) {
+                               int rows_per_thread, int add_input, int act, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "short_conv: activation code %d is unknown", act);
   if (taps < 1 || taps > CONV_MAX_TAPS) return cima_fail(CIMA_E_SIZE, "short_conv: %d taps are outside 1..%d", taps, CONV_MAX_TAPS);
   if (C <= 0 || n_seqs <= 0) return cima_fail(CIMA_E_SIZE, "short_conv: %d channels and %d sequences must be positive", C, n_seqs);
   if (one_row && T != n_seqs) return cima_fail(CIMA_E_ARG, "short_conv: %d rows are not one for each of %d sequences", T, n_seqs);
@@ -257,12 +260,12 @@ extern "C" int cima_short_conv(const void* h, int dtype, const float* w, void* s
   else if (rows_per_thread != 0) return cima_fail(CIMA_E_ARG, "short_conv: %d rows a thread; 0 (chosen here), 1, 2, 4 or 8 are possible", rows_per_thread);
 #define RUN(TA) { \
     int rc_; \
-    if (one_row) rc_ = cima_launch(k_short_conv<TA, true>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
-    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 8) rc_ = cima_launch(k_short_conv_rows<TA, 8>, dim3((T + 7) / 8, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps); \
-    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 4) rc_ = cima_launch(k_short_conv_rows<TA, 4>, dim3((T + 3) / 4, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps); \
-    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 2) rc_ = cima_launch(k_short_conv_rows<TA, 2>, dim3((T + 1) / 2, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps); \
-    else if (wide) rc_ = cima_launch(k_short_conv_wide<TA>, dim3(T, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
-    else rc_ = cima_launch(k_short_conv<TA, false>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps); \
+    if (one_row) rc_ = cima_launch(k_short_conv<TA, true>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps, add_input, act); \
+    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 8) rc_ = cima_launch(k_short_conv_rows<TA, 8>, dim3((T + 7) / 8, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps, add_input, act); \
+    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 4) rc_ = cima_launch(k_short_conv_rows<TA, 4>, dim3((T + 3) / 4, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps, add_input, act); \
+    else if (wide && taps <= CONV_FEW_TAPS && rows_each == 2) rc_ = cima_launch(k_short_conv_rows<TA, 2>, dim3((T + 1) / 2, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, T, C, taps, add_input, act); \
+    else if (wide) rc_ = cima_launch(k_short_conv_wide<TA>, dim3(T, (unsigned)((C / ConvVec<TA>::N + CONV_THREADS - 1) / CONV_THREADS)), block, (size_t)0, stream, 1, (const TA*)h, w, (const TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps, add_input, act); \
+    else rc_ = cima_launch(k_short_conv<TA, false>, dim3(T, cy), block, (size_t)0, stream, 1, (const TA*)h, w, (TA*)state, row_seq, seq_slot, seq_first_row, (TA*)u, C, taps, add_input, act); \
     if (rc_) return rc_; \
     if (!one_row && taps > 1) { rc_ = cima_launch(k_short_conv_state<TA>, dim3(n_seqs, cy), block, (size_t)0, stream, 1, (const TA*)h, (TA*)state, seq_slot, seq_first_row, C, taps); if (rc_) return rc_; } }
   if (dtype == CIMA_F32) RUN(float)

@@ -60,6 +60,7 @@ class Model:
         self.config = None                                  # set by load_model
         self.step_rows = STEP_ROWS                          # a step of more rows runs in parts
         self.embedding: Optional[torch.Tensor] = None
+        self.bigram: Optional[torch.Tensor] = None          # the hashed bigram table, where the spec has one
         self.head: Optional[Linear] = None
         self.cache: Optional[KVCache] = None
 
@@ -67,6 +68,8 @@ class Model:
     def plan(self) -> Dict[str, TensorSpec]:
         s = self.spec
         p: Dict[str, TensorSpec] = {s.embed_name: TensorSpec((s.vocab, s.hidden))}
+        if s.embed_bigram is not None:
+            p[s.embed_bigram.name] = TensorSpec((s.embed_bigram.buckets + 1, s.hidden))
         for b in self.blocks:
             p.update(b.plan())
         if self.depth is not None:
@@ -92,6 +95,8 @@ class Model:
         if s.tie_head:
             self.head = Linear(self.embedding, None, self.rt)     # one copy on the device serves both
         del table
+        if s.embed_bigram is not None:
+            self.bigram = self.rt.matrix(tensors[s.embed_bigram.name]).to(self.embedding.dtype)
         for b in self.blocks:
             b.load(tensors)
         if self.depth is not None:
@@ -105,6 +110,8 @@ class Model:
         the 32 bits they were stored in, vectors in float32); stacked matrices come back as views of their rows."""
         s = self.spec
         out: Dict[str, torch.Tensor] = {s.embed_name: self.embedding}
+        if self.bigram is not None:
+            out[s.embed_bigram.name] = self.bigram
         for b in self.blocks:
             out.update(b.state())
         if self.depth is not None:
@@ -142,11 +149,23 @@ class Model:
         sched = self.spec.schedule
         shares = {site: self.spec.layers[layer].mixer.cache_from for site, layer in enumerate(sched)
                   if self.spec.layers[layer].mixer.cache_from is not None}
-        self.cache = KVCache([self.blocks[layer].cache_requests(site) for site, layer in enumerate(sched)],
+        self.cache = KVCache(self._cache_requests(),
                              max_tokens, self.spec.max_position,
                              self.rt.dtype, self.rt.device, page_size=page_size, max_seqs=max_seqs,
                              shares=shares, extra_state=extra_state)
         return self.cache
+
+    BIGRAM_STATE = "embed.bigram_prev"
+
+    def _cache_requests(self):
+        """What every site asks of the cache; the token before a sequence's next one (the bigram embedding's state,
+        one int32 a slot) is asked for with the first site, as state that belongs to a sequence's end."""
+        reqs = [list(self.blocks[layer].cache_requests(site)) for site, layer in enumerate(self.spec.schedule)]
+        if self.spec.embed_bigram is not None:
+            if not reqs:
+                reqs.append([])
+            reqs[0].append(StateRequest(self.BIGRAM_STATE, (), torch.int32))
+        return reqs
 
     def forecast(self, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = 64,
                  extra_state: Sequence[StateRequest] = ()):
@@ -155,7 +174,7 @@ class Model:
         sched = self.spec.schedule
         shares = [site for site, layer in enumerate(sched) if self.spec.layers[layer].mixer.cache_from is not None]
         widest = max([int(getattr(b, "scratch_row", lambda: 0)()) for b in self.blocks] + [self.spec.hidden])
-        return forecast(self.plan(), [self.blocks[layer].cache_requests(site) for site, layer in enumerate(sched)],
+        return forecast(self.plan(), self._cache_requests(),
                         self.rt.dtype, max_tokens, self.spec.hidden, self.spec.vocab, widest, page_size, shares,
                         extra_state, max_seqs or 0, streams=len(sched) + 2 if self.depth is not None else 1)
 
@@ -267,7 +286,11 @@ class Model:
         # folded into the products around them (few rows) or run together with the residual add (many rows).
         info = None
         order = [self.blocks[layer] for layer in s.schedule]
-        if batch.n_rows <= FOLDED_NORM_ROWS and not self.rt.full_precision:
+        if s.embed_bigram is not None:
+            g = s.embed_bigram
+            K_.embed_bigram(batch, self.embedding, self.bigram, x, s.embed_scale, g.buckets, g.mul_prev, g.mul_cur,
+                            self.cache.state[self.BIGRAM_STATE])
+        elif batch.n_rows <= FOLDED_NORM_ROWS and not self.rt.full_precision:
             ssq = self.rt.empty(batch.n_rows, 1, dtype=torch.float32)
             first = getattr(order[0], "mixer_norm", None) if order else self.final_norm
             if (getattr(first, "weight", None) is not None and first.spec.kind == "rmsnorm"
@@ -355,7 +378,11 @@ def load_model(folder: Optional[str] = None, dtype="bfloat16", max_tokens: int =
     else:
         raw = config.to_dict() if hasattr(config, "to_dict") else dict(config)
     entry = lookup_architecture(raw)
-    typed = entry.parse(raw)
+    if folder is not None and entry.parse_with_shapes is not None:
+        from ..weights.loader import tensor_shapes
+        typed = entry.parse_with_shapes(raw, tensor_shapes(folder))      # sizes that only the tensors' shapes give
+    else:
+        typed = entry.parse(raw)
     spec = entry.spec(typed)
     if folder is not None:
         spec = settle_head(spec, tensor_names(folder),

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 24
+ABI_VERSION = 25
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -67,19 +67,31 @@ _SIGNATURES = {
                              _i, _i, _i, _i, _vp],
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                             _f, _i, _i, _i, _vp],
-    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp],
-    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
-    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+                             _f, _i, _i, _i, _f, _vp],
+    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _f, _vp],
+    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
+    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _f, _vp],
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                 _f, _i, _vp, _i, _vp],
-    "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+                                 _f, _i, _vp, _i, _f, _vp],
+    "cima_short_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_dyt": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "cima_dyt_add": [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "cima_embed_bigram": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, ctypes.c_longlong, ctypes.c_longlong, _vp, _vp, _vp, _vp, _vp,
+                          _i, _vp],
+    "cima_recurrence": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_delta_prepare": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "cima_group_rmsnorm_gate": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
+    "cima_rms_mean": [_vp, _vp, _i, _vp, _i, _i, _f, _vp],
+    "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
+    "cima_moe_sort": [_vp, _i, _i, _vp, _vp, _vp, _vp],
+    "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_moe_combine": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp],
     "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_head_linear_append": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp,
                                 _i, _vp],
-    "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -408,7 +420,7 @@ class Kernels:
 
     def attention_plain(self, qkv: torch.Tensor, kv, row_pos, row_seq, seq_slot, seq_first_row, out: torch.Tensor,
                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int,
-                        from_cache: bool) -> None:
+                        from_cache: bool, sink: float = 0.0) -> None:
         self._need(qkv, "qkv", None, 2); self._need(out, "out", qkv.dtype, 2)
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim):
@@ -426,7 +438,7 @@ class Kernels:
                                                   row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                                                   seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                   n_heads, n_kv_heads, head_dim, scale, window,
-                                                  1 if from_cache else 0, planes, self._stream()), "attention_plain")
+                                                  1 if from_cache else 0, planes, sink, self._stream()), "attention_plain")
 
     def _attention_work(self, qkv, n_heads, n_kv_heads, head_dim, planes: int = 2):
         """(bytes, operations) of an attention launch while a step is profiled: the keys and values of the step's
@@ -457,32 +469,34 @@ class Kernels:
             torch.mm(a, w.t(), out=out)
 
     def attention(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                  head_dim: int, scale: float, window: int, from_cache: bool, after_append: bool = False) -> None:
+                  head_dim: int, scale: float, window: int, from_cache: bool, after_append: bool = False,
+                  sink: float = 0.0) -> None:
         """Attention of a step's rows: over the step's own keys (a prompt from position 0) or over the
         cache.  Chooses the kernel; every choice computes the same function.  ``after_append``: the kernel
-        launched just before wrote nothing but ``qkv`` and the newest position of each sequence in the cache."""
+        launched just before wrote nothing but ``qkv`` and the newest position of each sequence in the cache.
+        ``sink``: that many entries of score 0 that carry no value join every row's denominator (0: an ordinary softmax)."""
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and batch.n_rows == batch.n_seqs):
             return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
-                                         scale, window, batch.max_len, early=after_append)
+                                         scale, window, batch.max_len, early=after_append, sink=sink)
         many = (qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
                 and getattr(batch, "n_q_tiles_tc", 0) > 0 and getattr(batch, "max_rows", 0) >= TC_ATTENTION_MIN_LEN)
         if from_cache and many and kv.page_size == 64 and kv.storage.numel() // head_dim < 2 ** 31:
-            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, kv=kv)
+            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, kv=kv, sink=sink)
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
-            return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
+            return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
         if not from_cache and many:
-            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
+            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_prefill(qkv, batch.q_tile_seq, batch.q_tile_row0, batch.seq_first_row, out,
-                                          n_heads, n_kv_heads, head_dim, scale, window)
+                                          n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
-                             n_heads, n_kv_heads, head_dim, scale, window, from_cache)
+                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink=sink)
 
     def attention_prefill(self, qkv: torch.Tensor, tile_seq, tile_row0, seq_first_row, out: torch.Tensor,
-                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, sink: float = 0.0) -> None:
         """Flash attention of ragged prompts that start at position 0 (bf16, head_dim <= 128);
         ``tile_seq``/``tile_row0`` list the blocks of 64 query rows."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
@@ -494,11 +508,11 @@ class Kernels:
         if not self._admit("attention_prefill", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         self._check(self.lib.cima_attention_prefill(qkv.data_ptr(), qkv.shape[1], tile_seq.data_ptr(), tile_row0.data_ptr(),
                                                     seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
-                                                    tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window,
+                                                    tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, sink,
                                                     self._stream()), "attention_prefill")
 
     def attention_extend(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                         head_dim: int, scale: float, window: int) -> None:
+                         head_dim: int, scale: float, window: int, sink: float = 0.0) -> None:
         """Flash attention of sequences that bring several rows to a cache that already holds keys (bf16, pages of
         64, head_dim <= 128): the rows of sequence s stand at positions seq_len[s] - rows .. seq_len[s] - 1, and all
         keys, the step's own included, are read from the layer's pages.  ``batch`` brings the blocks of 64 rows."""
@@ -512,10 +526,10 @@ class Kernels:
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_seq.data_ptr(), batch.q_tile_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(), out.data_ptr(), out.shape[1],
-            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, kv.planes, self._stream()), "attention_extend")
+            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, kv.planes, sink, self._stream()), "attention_extend")
 
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                             head_dim: int, scale: float, window: int, kv=None) -> None:
+                             head_dim: int, scale: float, window: int, kv=None, sink: float = 0.0) -> None:
         """Flash attention of ragged prompts on the tcgen05 tensor cores (bf16, head_dim 64 or 128): blocks of 128
         query rows, both products with their results in tensor memory.  ``batch`` brings the blocks
         (``q_tile_tc_*``).  Without ``kv`` the sequences start at position 0 and the keys are the step's own rows;
@@ -535,17 +549,17 @@ class Kernels:
                 batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.storage.shape[0], kv.block_table.data_ptr(),
                 kv.block_table.shape[1], kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(),
                 out.data_ptr(), out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
-                self._error_flag.data_ptr(), kv.planes, self._stream()), "attention_extend_tc")
+                self._error_flag.data_ptr(), kv.planes, sink, self._stream()), "attention_extend_tc")
             return
         self._check(self.lib.cima_attention_prefill_tc(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_tc_seq.data_ptr(), batch.q_tile_tc_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), out.data_ptr(),
             out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
-            self._error_flag.data_ptr(), self._stream()), "attention_prefill_tc")
+            self._error_flag.data_ptr(), sink, self._stream()), "attention_prefill_tc")
 
     def attention_decode(self, qkv: torch.Tensor, kv, seq_slot, seq_len, out: torch.Tensor, n_heads: int,
                          n_kv_heads: int, head_dim: int, scale: float, window: int, max_len: int = 0,
-                         n_splits: Optional[int] = None, early: bool = False) -> None:
+                         n_splits: Optional[int] = None, early: bool = False, sink: float = 0.0) -> None:
         """One query per sequence over the paged cache (bf16, pages of 64, head_dim <= 128), keys split
         over ``n_splits`` blocks per (sequence, kv head).  ``max_len`` (0 = unknown) only bounds the
         number of splits chosen here.  ``early``: the kernel launched just before this one wrote neither
@@ -584,7 +598,7 @@ class Kernels:
             qkv.data_ptr(), qkv.shape[1], kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, seq_slot.data_ptr(), seq_len.data_ptr(), _ptr(part_o), _ptr(part_ml),
             out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, int(early),
-            kv.planes, self._stream()), "attention_decode")
+            kv.planes, sink, self._stream()), "attention_decode")
         if n_splits > 1:
             self.launches += 1
 
@@ -601,10 +615,12 @@ class Kernels:
 
     # ------------------------------------------------------------------ short convolution, depth average, latents
     def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], batch, out: torch.Tensor,
-                   rows_per_thread: int = 0) -> None:
+                   rows_per_thread: int = 0, add_input: bool = True, act: int = -1) -> None:
         """out[t] = h[t] + sum_j w[j, :] * h[t - taps + 1 + j] per channel, causal within each sequence of the
         step; what lies before the step's rows comes from ``state`` [slots, taps - 1, C] (the sequences' last
-        inputs), which is brought up to date.  ``w`` [taps, C] float32 (tap by tap); h, out, state of one dtype."""
+        inputs), which is brought up to date.  ``w`` [taps, C] float32 (tap by tap); h, out, state of one dtype.
+        ``add_input`` False leaves h[t] out of the sum (a plain convolution); ``act`` >= 0 applies that entry of
+        ``ACTIVATIONS`` to the sum."""
         self._need(h, "h", None, 2); self._need(w, "w", torch.float32, 2); self._need(out, "out", h.dtype, 2)
         T, C = h.shape
         taps = w.shape[0]
@@ -619,7 +635,7 @@ class Kernels:
         self._check(self.lib.cima_short_conv(h.data_ptr(), dtype_code(h.dtype), w.data_ptr(), _ptr(state if taps > 1 else None),
                                              batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(), batch.seq_first_row.data_ptr(),
                                              out.data_ptr(), T, batch.n_seqs, C, taps, int(one_row), rows_per_thread,
-                                             self._stream()), "short_conv")
+                                             int(add_input), act, self._stream()), "short_conv")
         if not one_row and taps > 1:
             self.launches += 1
 
@@ -707,6 +723,206 @@ class Kernels:
             return
         self._check(self.lib.cima_head_linear(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), T, heads, N, K,
                                               a.stride(0), out.stride(0), self._stream()), "head_linear")
+
+    # ------------------------------------------------------------------ Dynamic Tanh, bigram embedding
+    def dyt(self, x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+        """out = tanh(alpha * x) * w + b: x float32 [T, H], alpha one float32 value on the device, w and b [H]."""
+        self._need(x, "x", torch.float32, 2); self._need(alpha, "alpha", torch.float32); self._need(w, "w", torch.float32, 1)
+        self._need(b, "b", torch.float32, 1); self._need(out, "out", None, 2)
+        T, H = x.shape
+        if alpha.numel() != 1 or w.numel() != H or b.numel() != H or tuple(out.shape) != (T, H):
+            raise KernelError(f"dyt: x {tuple(x.shape)}, alpha {tuple(alpha.shape)}, w {tuple(w.shape)}, b {tuple(b.shape)}, out "
+                              f"{tuple(out.shape)} do not agree")
+        if not self._admit("dyt", T * H * (4 + out.element_size())): return
+        self._check(self.lib.cima_dyt(x.data_ptr(), alpha.data_ptr(), w.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                      dtype_code(out.dtype), T, H, self._stream()), "dyt")
+
+    def dyt_add(self, x: torch.Tensor, y: torch.Tensor, norm, mult: float, next_norm=None, h: Optional[torch.Tensor] = None) -> None:
+        """x += mult * (tanh(a1 * y) * w1 + b1) with ``norm`` = (a1, w1, b1); with ``next_norm`` = (a2, w2, b2) also
+        h = tanh(a2 * x) * w2 + b2 of the updated rows.  x and y float32 [T, H]."""
+        self._need(x, "x", torch.float32, 2); self._need(y, "y", torch.float32, 2)
+        T, H = x.shape
+        a1, w1, b1 = norm
+        for n, t in (("alpha", a1), ("w", w1), ("b", b1)):
+            self._need(t, n, torch.float32)
+        if y.shape != x.shape or a1.numel() != 1 or w1.numel() != H or b1.numel() != H:
+            raise KernelError(f"dyt_add: x {tuple(x.shape)}, y {tuple(y.shape)} and the norm's tensors do not agree")
+        second = (None, None, None, None, F32)
+        if next_norm is not None:
+            a2, w2, b2 = next_norm
+            for n, t in (("alpha", a2), ("w", w2), ("b", b2)):
+                self._need(t, n, torch.float32)
+            self._need(h, "h", None, 2)
+            if a2.numel() != 1 or w2.numel() != H or b2.numel() != H or tuple(h.shape) != (T, H):
+                raise KernelError("dyt_add: the second norm's tensors and its output do not fit the rows")
+            second = (a2.data_ptr(), w2.data_ptr(), b2.data_ptr(), h.data_ptr(), dtype_code(h.dtype))
+        if not self._admit("dyt_add", T * H * (12 + (h.element_size() if h is not None else 0))): return
+        self._check(self.lib.cima_dyt_add(x.data_ptr(), y.data_ptr(), a1.data_ptr(), w1.data_ptr(), b1.data_ptr(), mult,
+                                          *second, T, H, self._stream()), "dyt_add")
+
+    def embed_bigram(self, batch, table: torch.Tensor, bigram: torch.Tensor, x: torch.Tensor, scale: float, buckets: int,
+                     mul_prev: int, mul_cur: int, prev_state: torch.Tensor) -> None:
+        """x[t] = scale * table[tok_t] + bigram[(tok_(t-1) * mul_prev + tok_t * mul_cur) mod buckets], row ``buckets`` at a
+        sequence's first position; the token before a step's rows is ``prev_state`` [slots] int32, brought up to date."""
+        self._need(table, "table", None, 2); self._need(bigram, "bigram", table.dtype, 2); self._need(x, "x", torch.float32, 2)
+        self._need(prev_state, "prev_state", torch.int32, 1)
+        T, (V, H) = batch.n_rows, table.shape
+        if tuple(x.shape) != (T, H) or tuple(bigram.shape) != (buckets + 1, H):
+            raise KernelError(f"embed_bigram: x {tuple(x.shape)}, table {tuple(table.shape)}, bigram {tuple(bigram.shape)} and "
+                              f"{buckets} buckets do not agree")
+        one_row = batch.n_rows == batch.n_seqs
+        if not self._admit("embed_bigram", T * H * (2 * table.element_size() + 4)): return
+        self._check(self.lib.cima_embed_bigram(batch.tokens.data_ptr(), table.data_ptr(), bigram.data_ptr(), dtype_code(table.dtype),
+                                               x.data_ptr(), T, batch.n_seqs, H, scale, buckets, mul_prev, mul_cur,
+                                               batch.row_pos.data_ptr(), batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(),
+                                               batch.seq_first_row.data_ptr(), prev_state.data_ptr(), int(one_row),
+                                               self._stream()), "embed_bigram")
+        if not one_row:
+            self.launches += 1
+
+    # ------------------------------------------------------------------ recurrent mixers
+    def recurrence(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, batch, out: torch.Tensor,
+                   heads: int, kv_heads: int, dim: int, vdim: int, g: Optional[torch.Tensor] = None,
+                   beta: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None) -> None:
+        """A linear recurrence over the step's rows, sequence by sequence, with the state S [slots, heads, dim, vdim]
+        (float32) carried on.  With ``decay`` [heads]: S <- d S + k v^T, o = S^T q, and q, k, v (one dtype) pass SiLU.
+        With ``g`` [T, heads * dim] and ``beta`` [T, heads]: the gated delta rule on prepared float32 q and k
+        ([T, kv_heads * dim]).  q, k, v may be column slices of wider matrices; out [T, heads * vdim] float32."""
+        delta = g is not None
+        self._need(state, "state", torch.float32, 4); self._need(out, "out", torch.float32, 2)
+        T = batch.n_rows
+        for n, t in (("q", q), ("k", k), ("v", v)):
+            if t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != T or not t.is_cuda:
+                raise KernelError(f"recurrence: {n} {tuple(t.shape)} must be GPU rows of the step with unit column stride")
+        if (tuple(state.shape[1:]) != (heads, dim, vdim) or tuple(out.shape) != (T, heads * vdim) or q.shape[1] != kv_heads * dim
+                or k.shape[1] != kv_heads * dim or v.shape[1] != heads * vdim or q.dtype is not k.dtype):
+            raise KernelError(f"recurrence: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, state {tuple(state.shape)}, "
+                              f"out {tuple(out.shape)} do not agree with {heads} heads on {kv_heads} of {dim} x {vdim}")
+        if delta:
+            self._need(g, "g", torch.float32, 2); self._need(beta, "beta", torch.float32, 2)
+            if q.dtype is not torch.float32 or tuple(g.shape) != (T, heads * dim) or tuple(beta.shape) != (T, heads):
+                raise KernelError("recurrence: the delta rule takes float32 q and k, g [T, heads * dim] and beta [T, heads]")
+        else:
+            self._need(decay, "decay", torch.float32, 1)
+            if decay.numel() != heads or q.dtype is not v.dtype:
+                raise KernelError("recurrence: the decay rule takes q, k, v of one dtype and one decay a head")
+        if not self._admit("recurrence[delta]" if delta else "recurrence[decay]",
+                           batch.n_seqs * heads * dim * vdim * 8 + T * (2 * kv_heads * dim * q.element_size() + heads * vdim * (4 + v.element_size())
+                                                                        + (heads * dim * 4 if delta else 0)),
+                           (8.0 if delta else 5.0) * T * heads * dim * vdim): return
+        self._check(self.lib.cima_recurrence(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                                             dtype_code(v.dtype), _ptr(g), _ptr(beta), _ptr(decay), state.data_ptr(),
+                                             batch.seq_slot.data_ptr(), batch.seq_first_row.data_ptr(), out.data_ptr(), T,
+                                             batch.n_seqs, heads, kv_heads, dim, vdim, int(delta), self._stream()), "recurrence")
+
+    def delta_prepare(self, qk: torch.Tensor, a: torch.Tensor, b: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
+                      qn: torch.Tensor, kn: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, heads: int, kv_heads: int,
+                      dim: int) -> None:
+        """What the gated delta rule needs of a token besides v, in float32: q and k as unit vectors per head (q also
+        times dim^-1/2), g = exp(-exp(A_log[h]) * softplus(a + dt_bias)) per head and key channel, beta = sigmoid(b).
+        ``qk`` [T, >= 2 * kv_heads * dim] holds q's heads and then k's; qk, a, b of one dtype, rows may be slices."""
+        T = qk.shape[0]
+        for n, t in (("qk", qk), ("a", a), ("b", b)):
+            if t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != T or t.dtype is not qk.dtype or not t.is_cuda:
+                raise KernelError(f"delta_prepare: {n} {tuple(t.shape)} {t.dtype} must be GPU rows of one dtype with unit column stride")
+        for n, t, shape in (("qn", qn, (T, kv_heads * dim)), ("kn", kn, (T, kv_heads * dim)), ("g", g, (T, heads * dim)),
+                            ("beta", beta, (T, heads))):
+            self._need(t, n, torch.float32, 2)
+            if tuple(t.shape) != shape:
+                raise KernelError(f"delta_prepare: {n} is {tuple(t.shape)}, expected {shape}")
+        self._need(A_log, "A_log", torch.float32, 1); self._need(dt_bias, "dt_bias", torch.float32, 1)
+        if (qk.shape[1] < 2 * kv_heads * dim or a.shape[1] != heads * dim or b.shape[1] != heads or A_log.numel() != heads
+                or dt_bias.numel() != heads * dim):
+            raise KernelError("delta_prepare: the inputs' widths do not agree with the heads and the key size")
+        if not self._admit("delta_prepare", T * (2 * kv_heads * dim + heads * dim + heads) * (4 + qk.element_size())): return
+        self._check(self.lib.cima_delta_prepare(qk.data_ptr(), qk.stride(0), a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                                                dtype_code(qk.dtype), A_log.data_ptr(), dt_bias.data_ptr(), qn.data_ptr(),
+                                                kn.data_ptr(), g.data_ptr(), beta.data_ptr(), T, heads, kv_heads, dim,
+                                                self._stream()), "delta_prepare")
+
+    def group_rmsnorm_gate(self, o: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, groups: int,
+                           eps: float) -> None:
+        """out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) over each of ``groups`` equal parts of a row: o float32
+        [T, groups * n]; w [n] (one weight for all groups) or [groups * n]; gate [T, groups * n] in out's dtype (rows may
+        be slices) or None."""
+        self._need(o, "o", torch.float32, 2); self._need(w, "w", torch.float32, 1); self._need(out, "out", None, 2)
+        T, W = o.shape
+        if groups <= 0 or W % groups or out.shape != o.shape or w.numel() not in (W // groups, W):
+            raise KernelError(f"group_rmsnorm_gate: o {tuple(o.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, {groups} groups do not agree")
+        n = W // groups
+        if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (T, W) or gate.dtype is not out.dtype):
+            raise KernelError(f"group_rmsnorm_gate: the gate {tuple(gate.shape)} {gate.dtype} must match the output")
+        shared = int(w.numel() == n and groups > 1)
+        if not self._admit("group_rmsnorm_gate", T * W * (4 + 2 * out.element_size())): return
+        self._check(self.lib.cima_group_rmsnorm_gate(o.data_ptr(), w.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                                     out.data_ptr(), dtype_code(out.dtype), T, groups, n, shared, eps,
+                                                     self._stream()), "group_rmsnorm_gate")
+
+    def rms_mean(self, ys, ws, x: torch.Tensor, eps: float) -> None:
+        """x += mean over the branches b of  y_b / sqrt(mean(y_b^2) + eps) * w_b:  y_b float32 [T, H], w_b [H], at most 4."""
+        self._need(x, "x", torch.float32, 2)
+        T, H = x.shape
+        if not (1 <= len(ys) <= 4) or len(ws) != len(ys):
+            raise KernelError(f"rms_mean: {len(ys)} branches with {len(ws)} weights; 1 to 4 of each are possible")
+        for y, w in zip(ys, ws):
+            self._need(y, "y", torch.float32, 2); self._need(w, "w", torch.float32, 1)
+            if y.shape != x.shape or w.numel() != H:
+                raise KernelError(f"rms_mean: a branch {tuple(y.shape)} / its weight {tuple(w.shape)} do not fit {tuple(x.shape)}")
+        if not self._admit("rms_mean", T * H * 4 * (len(ys) + 2)): return
+        yp = (ctypes.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
+        wp = (ctypes.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
+        self._check(self.lib.cima_rms_mean(yp, wp, len(ys), x.data_ptr(), T, H, eps, self._stream()), "rms_mean")
+
+    # ------------------------------------------------------------------ routed feed-forward
+    def moe_route(self, scores: torch.Tensor, top: int, groups: int, keep: int, scale: float, idx: torch.Tensor,
+                  wgt: torch.Tensor) -> None:
+        """``scores`` float32 [T, E] holds the router's logits (it is scratch afterwards).  s = sigmoid(logits); the
+        experts form ``groups`` equal groups of neighbours, a group's score is the sum of its two best, the best
+        ``keep`` groups stay, and the ``top`` best experts among them are chosen: idx [T, top] int32, and their weights
+        s / (sum of the chosen s + 1e-20) * scale in wgt [T, top] float32."""
+        self._need(scores, "scores", torch.float32, 2); self._need(idx, "idx", torch.int32, 2); self._need(wgt, "wgt", torch.float32, 2)
+        T, E = scores.shape
+        if tuple(idx.shape) != (T, top) or tuple(wgt.shape) != (T, top):
+            raise KernelError(f"moe_route: idx {tuple(idx.shape)} / wgt {tuple(wgt.shape)} are not {(T, top)}")
+        if not self._admit("moe_route", T * (E * 8 + top * 8)): return
+        self._check(self.lib.cima_moe_route(scores.data_ptr(), T, E, top, groups, keep, scale, idx.data_ptr(), wgt.data_ptr(),
+                                            self._stream()), "moe_route")
+
+    def moe_experts(self, h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
+                    x: torch.Tensor, act: int = 0) -> None:
+        """x[t] += sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
+        gate_up [E, 2 ff, H] (an expert's gate rows, then its up rows), down [E, H, ff]; x float32 [T, H].  Four launches:
+        the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum."""
+        self._need(h, "h", None, 2); self._need(gate_up, "gate_up", None, 3); self._need(down, "down", gate_up.dtype, 3)
+        self._need(idx, "idx", torch.int32, 2); self._need(wgt, "wgt", torch.float32, 2); self._need(x, "x", torch.float32, 2)
+        T, H = h.shape
+        E, ff2, _ = gate_up.shape
+        ff, top = ff2 // 2, idx.shape[1]
+        if (gate_up.shape[2] != H or tuple(down.shape) != (E, H, ff) or idx.shape[0] != T or wgt.shape != idx.shape
+                or tuple(x.shape) != (T, H)):
+            raise KernelError(f"moe_experts: h {tuple(h.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, idx "
+                              f"{tuple(idx.shape)}, x {tuple(x.shape)} do not agree")
+        P = T * top
+        dev = h.device
+        meta = torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
+        offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
+        z = torch.empty((P, ff), dtype=h.dtype, device=dev)
+        y = torch.empty((P, H), dtype=torch.float32, device=dev)
+        wb = gate_up.element_size()
+        touched = min(E, P)
+        if self._admit("moe_sort", P * 8):
+            self._check(self.lib.cima_moe_sort(idx.data_ptr(), P, E, offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(),
+                                               self._stream()), "moe_sort")
+        if self._admit("moe_gemm[gate|up]", touched * 2 * ff * H * wb + P * (H + ff) * h.element_size(), 4.0 * P * ff * H):
+            self._check(self.lib.cima_moe_gemm(h.data_ptr(), dtype_code(h.dtype), h.stride(0), gate_up.data_ptr(),
+                                               dtype_code(gate_up.dtype), z.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
+                                               perm.data_ptr(), P, E, top, ff, H, 0, act, self._stream()), "moe_gemm")
+        if self._admit("moe_gemm[down]", touched * ff * H * wb + P * (ff * h.element_size() + H * 4), 2.0 * P * ff * H):
+            self._check(self.lib.cima_moe_gemm(z.data_ptr(), dtype_code(z.dtype), ff, down.data_ptr(), dtype_code(down.dtype),
+                                               y.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(), P, E, top,
+                                               H, ff, 1, 0, self._stream()), "moe_gemm")
+        if self._admit("moe_combine", P * H * 4 + T * H * 8):
+            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), x.data_ptr(), T, top, H, self._stream()), "moe_combine")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:

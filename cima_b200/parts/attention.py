@@ -6,7 +6,11 @@ Formulas and order as the reference's layer loop, steps 2-7 (src/models/transfor
 bias before rotation, rotation before caching, scale = spec.scale, head h reads kv head
 h / (heads / kv_heads), no output bias unless the spec says so.
 
-Every size (heads, kv heads, head_dim, window, scale, bias flags) is a field of the spec.
+Every size (heads, kv heads, head_dim, window, scale, bias flags) is a field of the spec.  Two more are ``params``:
+``v_dim``, a value size that differs from the key size, and ``sink``, a number of entries of score 0 that carry no
+value and join every row's softmax denominator (1: p_j = exp(s_j) / (1 + sum exp(s))).  Keys and values live in the
+cache at one size, the larger of the two rounded up to 16: the rows of W_q, W_k, W_v (and the columns of W_o) that
+pad a head are zero, so scores and outputs are what the unpadded sizes give.
 """
 from __future__ import annotations
 
@@ -22,38 +26,58 @@ from .registry import build_position, register_mixer
 
 class Attention:
     def __init__(self, spec, layer: int, rt):
-        if spec.head_dim % 16 or spec.head_dim > 256:
-            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256")
+        self.dim, self.vdim = spec.head_dim, int(spec.params.get("v_dim", spec.head_dim))
+        self.sink = float(spec.params.get("sink", 0.0))
+        self.padded = self.dim != self.vdim or self.dim % 16 != 0
+        self.hd = -(-max(self.dim, self.vdim) // 16) * 16 if self.padded else self.dim      # a head's size in a step's rows and in the cache
+        if min(self.dim, self.vdim) <= 0 or self.hd > 256:
+            raise ValueError(f"attention: key size {self.dim} and value size {self.vdim} must be positive, at most 256")
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"attention: {spec.n_heads} heads are not a multiple of {spec.n_kv_heads} kv heads")
+        if self.padded and (spec.qkv_bias or spec.out_bias):
+            raise ValueError("attention: biases with padded heads are not implemented")
         self.spec, self.layer, self.rt = spec, layer, rt
         self.position = build_position(spec.position, rt)
-        self.qd = spec.n_heads * spec.head_dim
-        self.kvd = spec.n_kv_heads * spec.head_dim
+        self.qd = spec.n_heads * self.hd
+        self.kvd = spec.n_kv_heads * self.hd
         self.qkv = None
         self.out = None
 
     # ------------------------------------------------------------------ weights
     def plan(self, prefix: str, names: Dict[str, str]) -> Dict[str, TensorSpec]:
         s = self.spec
+        sfx = names.get("suffix", ".weight")
         p: Dict[str, TensorSpec] = {}
-        for key, rows in (("q", self.qd), ("k", self.kvd), ("v", self.kvd)):
-            p[f"{prefix}{names[key]}.weight"] = TensorSpec((rows, s.hidden))
+        for key, rows in (("q", s.n_heads * self.dim), ("k", s.n_kv_heads * self.dim), ("v", s.n_kv_heads * self.vdim)):
+            p[f"{prefix}{names[key]}{sfx}"] = TensorSpec((rows, s.hidden))
             if s.qkv_bias:
                 p[f"{prefix}{names[key]}.bias"] = TensorSpec((rows,))
-        p[f"{prefix}{names['o']}.weight"] = TensorSpec((s.hidden, self.qd))
+        p[f"{prefix}{names['o']}{sfx}"] = TensorSpec((s.hidden, s.n_heads * self.vdim))
         if s.out_bias:
             p[f"{prefix}{names['o']}.bias"] = TensorSpec((s.hidden,))
         return p
 
+    def _pad_rows(self, t: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """[heads * size, K] -> [heads * hd, K]: every head's rows followed by zero rows up to the cache's head size."""
+        if size == self.hd:
+            return t
+        out = torch.zeros((heads, self.hd, t.shape[1]), dtype=t.dtype, device=t.device)
+        out[:, :size] = t.view(heads, size, t.shape[1])
+        return out.view(heads * self.hd, t.shape[1])
+
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
         s = self.spec
+        sfx = names.get("suffix", ".weight")
         bias = None
         if s.qkv_bias:
             bias = torch.cat([tensors[f"{prefix}{names[k]}.bias"].float() for k in ("q", "k", "v")])
-        self.qkv = Linear([tensors[f"{prefix}{names[k]}.weight"] for k in ("q", "k", "v")], bias, self.rt)
+        sizes = {"q": (s.n_heads, self.dim), "k": (s.n_kv_heads, self.dim), "v": (s.n_kv_heads, self.vdim)}
+        self.qkv = Linear([self._pad_rows(tensors[f"{prefix}{names[k]}{sfx}"], *sizes[k]) for k in ("q", "k", "v")], bias, self.rt)
         ob = tensors[f"{prefix}{names['o']}.bias"] if s.out_bias else None
-        self.out = Linear(tensors[f"{prefix}{names['o']}.weight"], ob, self.rt)
+        wo = tensors[f"{prefix}{names['o']}{sfx}"]
+        if self.vdim != self.hd:
+            wo = self._pad_rows(wo.t().contiguous(), s.n_heads, self.vdim).t().contiguous()
+        self.out = Linear(wo, ob, self.rt)
 
     def nbytes(self) -> int:
         return self.qkv.nbytes() + self.out.nbytes()
@@ -61,13 +85,17 @@ class Attention:
     def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
         """The tensors of ``plan`` back out of the stacked matrices, as they are kept on the device."""
         out: Dict[str, torch.Tensor] = {}
+        s, sfx = self.spec, names.get("suffix", ".weight")
         r = 0
-        for key, rows in (("q", self.qd), ("k", self.kvd), ("v", self.kvd)):
-            out[f"{prefix}{names[key]}.weight"] = self.qkv.weight[r:r + rows]
+        for key, rows, heads, size in (("q", self.qd, s.n_heads, self.dim), ("k", self.kvd, s.n_kv_heads, self.dim),
+                                       ("v", self.kvd, s.n_kv_heads, self.vdim)):
+            w = self.qkv.weight[r:r + rows]
+            out[f"{prefix}{names[key]}{sfx}"] = w if size == self.hd else w.view(heads, self.hd, -1)[:, :size].reshape(heads * size, -1)
             if self.qkv.bias is not None:
                 out[f"{prefix}{names[key]}.bias"] = self.qkv.bias[r:r + rows]
             r += rows
-        out[f"{prefix}{names['o']}.weight"] = self.out.weight
+        wo = self.out.weight
+        out[f"{prefix}{names['o']}{sfx}"] = wo if self.vdim == self.hd else wo.view(-1, s.n_heads, self.hd)[:, :, :self.vdim].reshape(wo.shape[0], -1)
         if self.out.bias is not None:
             out[f"{prefix}{names['o']}.bias"] = self.out.bias
         return out
@@ -83,13 +111,13 @@ class Attention:
         """Positions up to which this mixer's decode kernel takes another road than for long contexts (none if 0):
         the stepper records decode steps for such contexts apart (``StepBatch.max_len`` is their bound)."""
         from ..kernels import short_context
-        return short_context(self.spec.head_dim)
+        return short_context(self.hd)
 
     # ------------------------------------------------------------------ cache
     def cache_requests(self, site: int) -> List[object]:
         if self.spec.cache_from is not None:
             return []
-        return [KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)]
+        return [KVRequest(self.spec.n_kv_heads, self.hd, self.spec.window)]
 
     # ------------------------------------------------------------------ step
     takes_pending_norm = True      # h may be a NormedInput: the q/k/v product folds the norm in when it can
@@ -101,25 +129,29 @@ class Attention:
         writes = s.cache_from is None
         rows = h.shape[0]
         if (not batch.prefill and writes and self.qkv._skinny(rows) and kv.storage.dtype is torch.bfloat16
-                and self.position.rotary_dim == s.head_dim and hasattr(K_, "qkv_rope")):
+                and self.position.rotary_dim == self.hd and hasattr(K_, "qkv_rope")):
             # decoding: projection, rotation and the append to the cache as one kernel
             qkv = self.rt.empty(rows, self.qd + 2 * self.kvd)
             if self.qkv._folds(h, rows):
                 K_.qkv_rope(h.xw, self.qkv.weight, self.qkv.bias, qkv, self.position.inv_freq, batch.row_pos,
-                            batch.row_seq, batch.seq_slot, kv, s.n_heads, s.n_kv_heads, s.head_dim,
+                            batch.row_seq, batch.seq_slot, kv, s.n_heads, s.n_kv_heads, self.hd,
                             norm=(h.ssq, h.norm.spec.eps))
             else:
                 K_.qkv_rope(h.tensor() if hasattr(h, "tensor") else h, self.qkv.weight, self.qkv.bias, qkv,
                             self.position.inv_freq, batch.row_pos, batch.row_seq, batch.seq_slot, kv, s.n_heads,
-                            s.n_kv_heads, s.head_dim)
+                            s.n_kv_heads, self.hd)
         else:
             qkv = self.qkv.store(h)
             K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
-                           batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
+                           batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, self.hd)
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
-        K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache,
-                     after_append=True)
+        if self.sink:
+            K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, self.hd, s.scale, s.window, from_cache,
+                         after_append=True, sink=self.sink)
+        else:
+            K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, self.hd, s.scale, s.window, from_cache,
+                         after_append=True)
         return self.out.accumulate(att, x, next_norm)
 
 

@@ -1,6 +1,8 @@
 """Arrangement of a layer's parts.  ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x))
 (src/models/transformer.rs:1024-1319).  ``parallel``: h = norm(x); x += mixer(conv(h)) + feed_forward(h): one norm
-feeds both sublayers, the mixer optionally through a short causal convolution, the feed-forward optionally absent.  The block builds its parts from the spec through the
+feeds both sublayers, the mixer optionally through a short causal convolution, the feed-forward optionally absent.
+``sandwich``: a norm in front of and behind each sublayer, x += m * post(mixer(norm(x))); x += m * post(ffn(norm(x))) with
+the spec's ``residual_mult`` m; the feed-forward with its two norms may be absent.  The block builds its parts from the spec through the
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
@@ -174,5 +176,106 @@ class ParallelBlock:
         return None
 
 
+class SandwichBlock:
+    """x += m * post1(mixer(pre1(x))), then x += m * post2(feed_forward(pre2(x))): every sublayer stands between two
+    norms, and what it adds to the stream is scaled by ``residual_mult``.  A sublayer adds its output into a zeroed
+    float32 buffer (the parts' one interface: they add into the rows they are given), which the norm behind it reads;
+    where that norm is a Dynamic Tanh, it, the scaled residual sum and the norm in front of the next sublayer are one
+    kernel.  Any registered norm serves; one without ``tensors`` runs as separate launches."""
+
+    def __init__(self, spec, layer: int, rt):
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and (spec.ffn_norm is None or spec.ffn_post_norm is None)):
+            raise ValueError(f"layer {layer}: a sandwich block needs a norm in front of and behind each of its sublayers")
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.mult = float(spec.residual_mult)
+        self.mixer_norm = build_norm(spec.mixer_norm, rt)
+        self.mixer = build_mixer(spec.mixer, layer, rt)
+        self.mixer_post = build_norm(spec.mixer_post_norm, rt)
+        self.feed_forward = self.ffn_norm = self.ffn_post = None
+        if spec.feed_forward is not None:
+            self.ffn_norm = build_norm(spec.ffn_norm, rt)
+            self.feed_forward = build_feed_forward(spec.feed_forward, layer, rt)
+            self.ffn_post = build_norm(spec.ffn_post_norm, rt)
+
+    def _named(self):
+        s = self.spec
+        sfx = s.names.get("suffix", ".weight")
+        out = [(self.mixer_norm, (f"{s.prefix}{s.names['mixer_norm']}{sfx}",)), (self.mixer, (s.prefix, s.names)),
+               (self.mixer_post, (f"{s.prefix}{s.names['mixer_post_norm']}{sfx}",))]
+        if self.feed_forward is not None:
+            out += [(self.ffn_norm, (f"{s.prefix}{s.names['ffn_norm']}{sfx}",)), (self.feed_forward, (s.prefix, s.names)),
+                    (self.ffn_post, (f"{s.prefix}{s.names['ffn_post_norm']}{sfx}",))]
+        return out
+
+    def plan(self) -> Dict[str, TensorSpec]:
+        p: Dict[str, TensorSpec] = {}
+        for part, args in self._named():
+            p.update(part.plan(*args))
+        return p
+
+    def load(self, tensors) -> None:
+        for part, args in self._named():
+            part.load(tensors, *args)
+
+    def state(self) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        for part, args in self._named():
+            if not hasattr(part, "state"):
+                raise NotImplementedError(f"{type(part).__name__} of layer {self.layer} offers no state(): its tensors "
+                                          f"cannot be given back by name")
+            out.update(part.state(*args))
+        return out
+
+    def cache_requests(self, site: int) -> List[object]:
+        return list(self.mixer.cache_requests(site))
+
+    def scratch_row(self) -> int:
+        parts = [p for p in (self.mixer, self.feed_forward) if p is not None]
+        return max(int(getattr(p, "scratch_row", lambda: 0)()) for p in parts) + 2 * self.spec.mixer.hidden
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p, _ in self._named())
+
+    def nbytes(self) -> int:
+        return sum(p.nbytes() for p, _ in self._named())
+
+    def _close(self, x, y, post, next_norm):
+        """x += m * post(y); returns what the norm that reads x next gives, when it ran in the same kernel."""
+        K_ = self.rt.kernels
+        if hasattr(post, "tensors") and hasattr(K_, "dyt_add"):
+            if next_norm is not None and hasattr(next_norm, "tensors"):
+                h = self.rt.empty(*x.shape)
+                K_.dyt_add(x, y, post.tensors, self.mult, next_norm.tensors, h)
+                return h
+            K_.dyt_add(x, y, post.tensors, self.mult)
+            return None
+        p = post(y)
+        if self.mult != 1.0:
+            p = p * self.mult
+        K_.add_residual(x, p)
+        return None
+
+    def forward(self, x: torch.Tensor, batch, cache, site: int, info=None, next_norm=None):
+        from .norm import RowsInfo
+        if info is not None and getattr(info, "norm", None) is self.mixer_norm and info.h is not None:
+            h = info.h
+        else:
+            h = self.mixer_norm(x)
+        y = torch.zeros_like(x)
+        self.mixer.forward(h, y, batch, cache, site)
+        if self.feed_forward is None:
+            h = self._close(x, y, self.mixer_post, next_norm)
+            return RowsInfo(norm=next_norm, h=h) if h is not None else None
+        h = self._close(x, y, self.mixer_post, self.ffn_norm)
+        if h is None:
+            h = self.ffn_norm(x)
+        y.zero_()
+        self.feed_forward.forward(h, y, batch)
+        h = self._close(x, y, self.ffn_post, next_norm)
+        return RowsInfo(norm=next_norm, h=h) if h is not None else None
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)
 register_block("parallel", ParallelBlock)

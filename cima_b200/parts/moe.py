@@ -1,0 +1,99 @@
+"""A routed feed-forward (kind ``moe``): ``experts`` small gated feed-forward layers of which every token uses ``top``.
+
+    s = sigmoid(W_router h)                                   router logits and scores in float32
+    the experts form ``groups`` equal groups of neighbours; a group's score is the sum of its two largest s; only
+    experts of the best ``keep`` groups can be chosen; of those, the ``top`` with the largest s are
+    weights  w_e = s_e / (sum of the chosen s + 1e-20) * scale
+    y = sum_e  w_e * W_down[e] (act(W_gate[e] h) * (W_up[e] h))
+
+The experts' matrices are kept stacked, [E, 2 ff, H] (an expert's gate rows, then its up rows) and [E, H, ff]; a step
+sorts its (row, choice) pairs by expert on the device and runs two grouped products over tiles of one expert's pairs,
+so nothing of the routing is read on the host.  Tensors: ``router`` and, per expert j, ``e<j>.gate``, ``e<j>.up``,
+``e<j>.down`` under the feed-forward's stem (names["experts"]).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .linear import Linear
+from .registry import register_feed_forward
+
+
+class RoutedExperts:
+    def __init__(self, spec, layer: int, rt):
+        from ..kernels import ACTIVATIONS
+        p = spec.params
+        self.E, self.top = int(p["experts"]), int(p["top"])
+        self.groups, self.keep, self.scale = int(p.get("groups", 1)), int(p.get("keep", p.get("groups", 1))), float(p.get("scale", 1.0))
+        if spec.activation not in ACTIVATIONS:
+            raise ValueError(f"moe: activation '{spec.activation}' is not one of {sorted(ACTIVATIONS)}")
+        if self.E <= 0 or self.groups <= 0 or self.E % self.groups or not (0 < self.keep <= self.groups):
+            raise ValueError(f"moe: {self.E} experts in {self.groups} groups of which {self.keep} stay are not a valid routing")
+        if not (0 < self.top <= self.keep * (self.E // self.groups)):
+            raise ValueError(f"moe: {self.top} choices among the {self.keep * (self.E // self.groups)} experts that stay")
+        if self.E > 1024 or self.groups > 64:
+            raise ValueError("moe: at most 1024 experts in at most 64 groups")
+        self.act = ACTIVATIONS[spec.activation]
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.router = self.gate_up = self.down = None
+
+    def _n(self, prefix, names, tail):
+        return f"{prefix}{names['experts']}{tail}{names.get('suffix', '.weight')}"
+
+    def plan(self, prefix: str, names: Dict[str, str]) -> Dict[str, TensorSpec]:
+        s = self.spec
+        p = {self._n(prefix, names, "router"): TensorSpec((self.E, s.hidden), std=0.1)}
+        for j in range(self.E):
+            p[self._n(prefix, names, f"e{j}.gate")] = TensorSpec((s.intermediate, s.hidden))
+            p[self._n(prefix, names, f"e{j}.up")] = TensorSpec((s.intermediate, s.hidden))
+            p[self._n(prefix, names, f"e{j}.down")] = TensorSpec((s.hidden, s.intermediate))
+        return p
+
+    def load(self, tensors, prefix: str, names: Dict[str, str]) -> None:
+        s, rt = self.spec, self.rt
+        self.router = Linear(tensors[self._n(prefix, names, "router")], None, rt)
+        ff, H = s.intermediate, s.hidden
+        first = rt.matrix(tensors[self._n(prefix, names, "e0.gate")])
+        self.gate_up = torch.empty((self.E, 2 * ff, H), dtype=first.dtype, device=rt.device)
+        self.down = torch.empty((self.E, H, ff), dtype=first.dtype, device=rt.device)
+        for j in range(self.E):
+            self.gate_up[j, :ff].copy_(first if j == 0 else tensors[self._n(prefix, names, f"e{j}.gate")])
+            self.gate_up[j, ff:].copy_(tensors[self._n(prefix, names, f"e{j}.up")])
+            self.down[j].copy_(tensors[self._n(prefix, names, f"e{j}.down")])
+
+    def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
+        ff = self.spec.intermediate
+        out = {self._n(prefix, names, "router"): self.router.weight}
+        for j in range(self.E):
+            out[self._n(prefix, names, f"e{j}.gate")] = self.gate_up[j, :ff]
+            out[self._n(prefix, names, f"e{j}.up")] = self.gate_up[j, ff:]
+            out[self._n(prefix, names, f"e{j}.down")] = self.down[j]
+        return out
+
+    def nbytes(self) -> int:
+        """Bytes a decode step reads: the router and, of the experts, the ``top`` that one token uses."""
+        per = (self.gate_up[0].numel() + self.down[0].numel()) * self.gate_up.element_size()
+        return self.router.nbytes() + self.top * per
+
+    def scratch_row(self) -> int:
+        return self.top * (2 * self.spec.intermediate + 2 * self.spec.hidden) + self.E
+
+    graph_safe = True
+
+    def forward(self, h, x: torch.Tensor, batch, next_norm=None):
+        K_, rt = self.rt.kernels, self.rt
+        if hasattr(h, "tensor"):
+            h = h.tensor()
+        rows = h.shape[0]
+        scores = self.router.logits(h)                                # float32 [rows, E]
+        idx = rt.empty(rows, self.top, dtype=torch.int32)
+        wgt = rt.empty(rows, self.top, dtype=torch.float32)
+        K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt)
+        K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act)
+        return None
+
+
+register_feed_forward("moe", RoutedExperts)

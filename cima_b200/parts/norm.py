@@ -69,4 +69,41 @@ class RMSNorm:
         return out
 
 
+class DynamicTanh:
+    """y = tanh(alpha * x) * w + b: a norm that computes no mean and no variance.  ``alpha`` is one stored scalar (it
+    stays on the device: a recorded step reads it there), w and b vectors; tensors ``name``, ``name.b``, ``name.alpha``.
+    The spec's eps is not used.  Everything float32, one rounding at the store."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.weight = self.bias = self.alpha = None
+
+    def plan(self, name: str) -> Dict[str, TensorSpec]:
+        return {name: TensorSpec((self.spec.size,), init="ones_normal"), name + ".b": TensorSpec((self.spec.size,), std=0.05),
+                name + ".alpha": TensorSpec((), init="ones_normal")}
+
+    def load(self, tensors, name: str) -> None:
+        self.weight = self.rt.vector(tensors[name])
+        self.bias = self.rt.vector(tensors[name + ".b"])
+        self.alpha = self.rt.vector(tensors[name + ".alpha"]).reshape(1)
+
+    def nbytes(self) -> int:
+        return (self.weight.numel() + self.bias.numel() + 1) * 4
+
+    def state(self, name: str) -> Dict[str, torch.Tensor]:
+        return {name: self.weight, name + ".b": self.bias, name + ".alpha": self.alpha.reshape(())}
+
+    graph_safe = True
+
+    @property
+    def tensors(self):
+        return (self.alpha, self.weight, self.bias)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        out = self.rt.empty(*x.shape)
+        self.rt.kernels.dyt(x, self.alpha, self.weight, self.bias, out)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("dyt", DynamicTanh)

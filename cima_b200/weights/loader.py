@@ -69,6 +69,16 @@ def tensor_names(folder: str) -> List[str]:
             sf.close()
 
 
+def tensor_shapes(folder: str) -> Dict[str, Tuple[int, ...]]:
+    """{name: shape} of all tensors that the folder's safetensors files hold (headers only)."""
+    where = open_model_files(folder)
+    try:
+        return {n: tuple(f.tensors[stored]["shape"]) for n, (f, stored) in where.items()}
+    finally:
+        for sf in {id(f): f for f, _ in where.values()}.values():
+            sf.close()
+
+
 class TensorSource:
     """Tensors by name, fetched one at a time when a part asks for them (``source[name]``), so that loading holds
     one tensor on the host, not one checkpoint.  Counts the bytes of the tensors it handed out that are still alive

@@ -151,12 +151,13 @@ class ReferenceKernels:
             kv.storage[page, 0, :, off, :] = heads[r, n_heads:n_heads + n_kv_heads, :]
             kv.storage[page, 1, :, off, :] = heads[r, n_heads + n_kv_heads:, :]
 
-    def attention(self, qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, from_cache, after_append=False):
+    def attention(self, qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, from_cache, after_append=False,
+                  sink=0.0):
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
-                             n_heads, n_kv_heads, head_dim, scale, window, from_cache)
+                             n_heads, n_kv_heads, head_dim, scale, window, from_cache, sink)
 
     def attention_plain(self, qkv, kv, row_pos, row_seq, seq_slot, seq_first_row, out, n_heads, n_kv_heads,
-                        head_dim, scale, window, from_cache):
+                        head_dim, scale, window, from_cache, sink=0.0):
         T = qkv.shape[0]
         rep = n_heads // n_kv_heads
         vplane = int(getattr(kv, "planes", 2)) - 1 if from_cache else 1      # one plane: the values are the keys
@@ -182,7 +183,12 @@ class ReferenceKernels:
             for h in range(n_heads):
                 g = h // rep
                 s = (k[:, g, :] @ q[h]) * scale
-                w = torch.softmax(s, dim=0)
+                if sink:                                    # entries of score 0 without a value in the denominator
+                    m = torch.clamp(s.max(), min=0.0)
+                    e = torch.exp(s - m)
+                    w = e / (e.sum() + sink * torch.exp(-m))
+                else:
+                    w = torch.softmax(s, dim=0)
                 out[r, h * head_dim:(h + 1) * head_dim] = (w @ v[:, g, :]).to(out.dtype)
 
     # ------------------------------------------------------------------ sampling
@@ -214,7 +220,7 @@ class ReferenceKernels:
 
 
 # ---------------------------------------------------------------------- short convolution, depth average, latents
-def _short_conv(self, h, w, state, batch, out, rows_per_thread=0):
+def _short_conv(self, h, w, state, batch, out, rows_per_thread=0, add_input=True, act=-1):
     taps = w.shape[0]
     first = batch.seq_first_row
     hc = h.to(self.compute)
@@ -224,9 +230,11 @@ def _short_conv(self, h, w, state, batch, out, rows_per_thread=0):
         past = state[slot].to(self.compute) if taps > 1 else hc[:0]
         line = torch.cat([past, hc[lo:hi]])                      # the inputs from taps - 1 positions before the step on
         n = hi - lo
-        acc = hc[lo:hi].clone()
+        acc = hc[lo:hi].clone() if add_input else torch.zeros_like(hc[lo:hi])
         for j in range(taps):
             acc = acc + w[j].to(self.compute) * line[j:j + n]
+        if act >= 0:
+            acc = self.gate_act(acc, act)
         out[lo:hi] = acc.to(out.dtype)
         if taps > 1:
             state[slot] = line[n:].to(state.dtype)
@@ -271,3 +279,123 @@ ReferenceKernels.short_conv = _short_conv
 ReferenceKernels.depth_average = _depth_average
 ReferenceKernels.latent_append = _latent_append
 ReferenceKernels.head_linear = _head_linear
+
+
+# ---------------------------------------------------------------------- Dynamic Tanh, bigram embedding
+def _dyt(self, x, alpha, w, b, out):
+    out.copy_((torch.tanh(alpha.to(self.compute) * x.to(self.compute)) * w + b).to(out.dtype))
+
+
+def _dyt_add(self, x, y, norm, mult, next_norm=None, h=None):
+    a1, w1, b1 = norm
+    x.add_(mult * (torch.tanh(a1 * y) * w1 + b1))
+    if next_norm is not None:
+        a2, w2, b2 = next_norm
+        h.copy_((torch.tanh(a2 * x) * w2 + b2).to(h.dtype))
+
+
+def _embed_bigram(self, batch, table, bigram, x, scale, buckets, mul_prev, mul_cur, prev_state):
+    ids = batch.tokens
+    for r in range(batch.n_rows):
+        seq = int(batch.row_seq[r])
+        slot = int(batch.seq_slot[seq])
+        k = r - int(batch.seq_first_row[seq])
+        prev = int(ids[r - 1]) if k > 0 else int(prev_state[slot])
+        row = buckets if int(batch.row_pos[r]) == 0 else (prev * mul_prev + int(ids[r]) * mul_cur) % buckets
+        x[r] = table[int(ids[r])].float() * scale + bigram[row].float()
+    for s in range(batch.n_seqs):
+        prev_state[int(batch.seq_slot[s])] = int(ids[int(batch.seq_first_row[s + 1]) - 1])
+
+
+# ---------------------------------------------------------------------- recurrent mixers
+def _silu(z):
+    return z / (1.0 + torch.exp(-z))
+
+
+def _recurrence(self, q, k, v, state, batch, out, heads, kv_heads, dim, vdim, g=None, beta=None, decay=None):
+    delta = g is not None
+    T = batch.n_rows
+    qf, kf, vf = q.float().view(T, kv_heads, dim), k.float().view(T, kv_heads, dim), v.float().view(T, heads, vdim)
+    if not delta:
+        qf, kf, vf = _silu(qf), _silu(kf), _silu(vf)
+    share = heads // kv_heads
+    for s in range(batch.n_seqs):
+        lo, hi = int(batch.seq_first_row[s]), int(batch.seq_first_row[s + 1])
+        slot = int(batch.seq_slot[s])
+        for h in range(heads):
+            c = h // share
+            S = state[slot, h].clone()
+            for t in range(lo, hi):
+                if delta:
+                    S = g[t].view(heads, dim)[h][:, None] * S
+                    u = beta[t, h] * (vf[t, h] - S.T @ kf[t, c])
+                else:
+                    S = decay[h] * S
+                    u = vf[t, h]
+                S = S + torch.outer(kf[t, c], u)
+                out[t, h * vdim:(h + 1) * vdim] = S.T @ qf[t, c]
+            state[slot, h] = S
+
+
+def _delta_prepare(self, qk, a, b, A_log, dt_bias, qn, kn, g, beta, heads, kv_heads, dim):
+    T = qk.shape[0]
+    kd = kv_heads * dim
+    qf, kf = qk[:, :kd].float().view(T, kv_heads, dim), qk[:, kd:2 * kd].float().view(T, kv_heads, dim)
+    qn.copy_((qf / torch.sqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5).view(T, kd))
+    kn.copy_((kf / torch.sqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)).view(T, kd))
+    step = torch.nn.functional.softplus(a.float() + dt_bias).view(T, heads, dim)
+    g.copy_(torch.exp(-torch.exp(A_log)[None, :, None] * step).view(T, heads * dim))
+    beta.copy_(torch.sigmoid(b.float()))
+
+
+def _group_rmsnorm_gate(self, o, w, gate, out, groups, eps):
+    T, W = o.shape
+    n = W // groups
+    z = o.view(T, groups, n)
+    z = z / torch.sqrt((z * z).mean(-1, keepdim=True) + eps)
+    z = z * (w.view(1, 1, n) if w.numel() == n and groups > 1 else w.view(1, groups, n))
+    if gate is not None:
+        z = z * torch.sigmoid(gate.float().view(T, groups, n))
+    out.copy_(z.view(T, W).to(out.dtype))
+
+
+def _rms_mean(self, ys, ws, x, eps):
+    acc = torch.zeros_like(x)
+    for y, w in zip(ys, ws):
+        acc = acc + y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * w
+    x.add_(acc / len(ys))
+
+
+# ---------------------------------------------------------------------- routed feed-forward
+def _moe_route(self, scores, top, groups, keep, scale, idx, wgt):
+    T, E = scores.shape
+    per = E // groups
+    s = torch.sigmoid(scores)
+    for t in range(T):
+        gs = [float(s[t, gi * per:(gi + 1) * per].topk(min(2, per)).values.sum()) for gi in range(groups)]
+        best = sorted(range(groups), key=lambda gi: (-gs[gi], gi))[:keep]
+        allowed = [e for gi in best for e in range(gi * per, (gi + 1) * per)]
+        chosen = sorted(allowed, key=lambda e: (-float(s[t, e]), e))[:top]
+        w = torch.stack([s[t, e] for e in chosen])
+        idx[t] = torch.tensor(chosen, dtype=idx.dtype)
+        wgt[t] = w / (w.sum() + 1e-20) * scale
+    scores.copy_(s)
+
+
+def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0):
+    ff = gate_up.shape[1] // 2
+    hf = h.float()
+    for t in range(h.shape[0]):
+        acc = torch.zeros_like(x[t])
+        for j in range(idx.shape[1]):
+            e = int(idx[t, j])
+            gu = (gate_up[e].float() @ hf[t]).to(h.dtype).float()
+            z = (self.gate_act(gu[:ff], act) * gu[ff:]).to(h.dtype).float()
+            acc = acc + wgt[t, j] * (down[e].float() @ z)
+        x[t] += acc
+
+
+for _name, _fn in (("dyt", _dyt), ("dyt_add", _dyt_add), ("embed_bigram", _embed_bigram), ("recurrence", _recurrence),
+                   ("delta_prepare", _delta_prepare), ("group_rmsnorm_gate", _group_rmsnorm_gate), ("rms_mean", _rms_mean),
+                   ("moe_route", _moe_route), ("moe_experts", _moe_experts)):
+    setattr(ReferenceKernels, _name, _fn)
