@@ -62,10 +62,10 @@ G_A = config(300, 96, 1e-6, 1.3, 2.0, (61, 5, 3), [
 G_B = config(513, 100, 1e-5, 0.6, 5.0, (127, 31, 7), [
     parallel(3, 3, 16, 16, 0.25, None, 1, 8, 8, [0.8], moe(20, 3, 3, 1.5)),
     delta(1, 1, 24, 24, 1, 4, 4, None),
-    delta(3, 3, 8, 16, 4, 24, 8, moe(32, 12, 4, 1.5, groups=4, keep=3))])
+    delta(3, 3, 8, 16, 4, 24, 8, moe(32, 10, 3, 1.25, groups=5, keep=3))])
 # the sizes of the tensor-core attention kernels (heads of 64 and of 128) and a recurrence over 128 key channels
-G_C = config(640, 256, 1e-5, 0.7, 1.0, (1021, 3, 11), [
-    parallel(4, 2, 64, 64, 0.125, rot(64, 1000000.0, (4.0, 1.0, 4.0, 2048)), 4, 32, 64, [0.6, 0.9, 0.97, 0.999],
+G_C = config(640, 256, 1e-5, 0.85, 1.0, (509, 3, 11), [
+    parallel(4, 2, 64, 64, 0.125, rot(64, 200000.0, (3.0, 1.0, 8.0, 1024)), 4, 32, 64, [0.6, 0.9, 0.97, 0.995],
              moe(96, 8, 2, 1.0, groups=4, keep=2)),
     delta(2, 2, 128, 64, 4, 16, 16, moe(64, 4, 2, 2.5, groups=2, keep=2)),
     parallel(2, 1, 128, 128, 0.09, rot(32, 10000.0), 2, 64, 32, [0.95, 0.99], None)])

@@ -150,14 +150,14 @@ def test_plain_causal_taps_against_conv1d():
 
 def test_plain_route_keeps_to_the_best_groups():
     torch.manual_seed(5)
-    h, wr = torch.randn(40, 16, dtype=torch.float64), torch.randn(12, 16, dtype=torch.float64)
-    ids, ws = plain_route(h, wr, top=4, groups=4, keep=2, scale=1.5)
+    h, wr = torch.randn(40, 16, dtype=torch.float64), torch.randn(15, 16, dtype=torch.float64)
+    ids, ws = plain_route(h, wr, top=4, groups=5, keep=2, scale=1.25)
     s = torch.sigmoid(h @ wr.T)
     for t in range(40):
         groups = sorted({e // 3 for e in ids[t]})
-        score = [s[t, g * 3:(g + 1) * 3].topk(2).values.sum() for g in range(4)]
-        assert len(groups) <= 2 and set(groups) <= set(sorted(range(4), key=lambda g: -score[g])[:2])
-        assert math.isclose(float(ws[t].sum()), 1.5, rel_tol=1e-9) and len(set(ids[t])) == 4
+        score = [s[t, g * 3:(g + 1) * 3].topk(2).values.sum() for g in range(5)]
+        assert len(groups) <= 2 and set(groups) <= set(sorted(range(5), key=lambda g: -score[g])[:2])
+        assert math.isclose(float(ws[t].sum()), 1.25, rel_tol=1e-9) and len(set(ids[t])) == 4
     free, _ = plain_route(h, wr, top=4, groups=1, keep=1, scale=1.0)
     assert all(sorted(free[t]) == sorted(s[t].topk(4).indices.tolist()) for t in range(40))
 
