@@ -146,6 +146,8 @@ def design_bench(a) -> int:
         out = {"weight_bytes": model.weight_bytes(), "recorded": bool(st.use_graphs)}
         kv_bytes = sum(g.storage.element_size() * len(g.layers) * g.request.planes * g.request.n_kv_heads * g.request.head_dim
                        for g in model.cache.groups)
+        # state of fixed size per sequence (a recurrence's matrix, a convolution's inputs): read and written every step
+        state_bytes = 2 * sum(t[0].numel() * t.element_size() for n, t in model.cache.state.items() if not n.startswith("sampler"))
         for batch in sorted({1, a.batch}):
             prompts = [rng.integers(0, V, size=a.prompt).tolist() for _ in range(batch)]
             slots = st.open(batch)
@@ -159,7 +161,8 @@ def design_bench(a) -> int:
             finally:
                 st.close(slots)
             ctx = a.prompt + 1 + warmup + steps / 2.0
-            gbs = (out["weight_bytes"] + batch * ctx * kv_bytes) / (secs / steps) / 1e9
+            wbytes = model.weight_bytes(rows=batch) if "rows" in model.weight_bytes.__code__.co_varnames else out["weight_bytes"]
+            gbs = (wbytes + batch * (ctx * kv_bytes + state_bytes)) / (secs / steps) / 1e9
             out[f"decode_b{batch}"] = {"tokens_per_s": batch * steps / secs, "ms_per_step": secs / steps * 1e3,
                                        "launches_per_step": lps, "hbm_frac": gbs / pk["hbm_gbs"]}
         T = 2048
@@ -228,7 +231,7 @@ def main(argv=None) -> int:
                     "defined on the default, Qwen2.5-7B)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--design", default=None, choices=["vunovik"], help="instead of the metric line: decode and prefill "
+    ap.add_argument("--design", default=None, choices=["vunovik", "gisirax"], help="instead of the metric line: decode and prefill "
                     "throughput of that design's shapes beside the Qwen2 shape of equal size (--sizes, --layers)")
     ap.add_argument("--sizes", default="1.5b,3b,7b", help="with --design: the shapes to measure (0.5b, 1.5b, 3b, 7b)")
     ap.add_argument("--per-kernel", action="store_true", help="instead of the metric line: every launch of one decode step "

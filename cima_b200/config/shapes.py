@@ -1,6 +1,8 @@
 """Known shapes of the Qwen2 dense decoder, for the random-weights mode (``cima random``), and shapes of the
 Vunovik decoder at the same widths, heads, feed-forward sizes and vocabularies (no trained model of that design
-exists; they serve measurements beside the Qwen2 shape of equal size).
+exists; they serve measurements beside the Qwen2 shape of equal size), and shapes of the Gisirax decoder at those
+widths: two delta-rule layers, then one layer of softmax attention beside a decay recurrence, every layer with routed
+experts of which a token uses as many values of a feed-forward's middle as the Qwen2 shape has.
 Every entry is a complete config.json; nothing here is read by the model code."""
 
 
@@ -23,10 +25,36 @@ def _vunovik(layers, width, heads, dim, rank, ff, vocab, taps=4):
             "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": out}
 
 
-# the Qwen2 shape that a Vunovik shape is measured beside
-TWINS = {"vunovik-0.5b": "qwen2.5-0.5b", "vunovik-1.5b": "qwen2.5-1.5b", "vunovik-3b": "qwen2.5-3b", "vunovik-7b": "qwen2.5-7b"}
+def _gisirax(layers, width, heads, kv_heads, dim, ff, vocab, experts=16, top=4, groups=4, keep=2, taps=4, rank=64):
+    """Layers 0, 1 of every three run the gated delta rule, layer 2 the two attentions side by side; ``top`` experts of
+    ``ff / top`` values each stand for the dense feed-forward of ``ff`` values."""
+    per = -(-ff // top // 64) * 64
+    mlp = {"kind": "moe", "expert": {"ff": per}, "router": {"experts": experts, "top": top, "scale": 1.0,
+                                                             "groups": {"count": groups, "keep": keep}}}
+    out = []
+    for i in range(layers):
+        if i % 3 == 2:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                    "rot": {"dims": dim, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            right = {"heads": heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, heads - 1)) for h in range(heads)]}
+            out.append({"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp})
+        else:
+            out.append({"type": "channel_delta", "mlp": mlp,
+                        "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": taps, "a_rank": rank, "g_rank": rank}})
+    return {"architecture": "Gisirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 1.0,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 127}}, "layers": out}
+
+
+# the Qwen2 shape that a Vunovik or Gisirax shape is measured beside
+TWINS = {"gisirax-0.5b": "qwen2.5-0.5b", "gisirax-1.5b": "qwen2.5-1.5b", "gisirax-3b": "qwen2.5-3b", "gisirax-7b": "qwen2.5-7b",
+         "vunovik-0.5b": "qwen2.5-0.5b", "vunovik-1.5b": "qwen2.5-1.5b", "vunovik-3b": "qwen2.5-3b", "vunovik-7b": "qwen2.5-7b"}
 
 SHAPES = {
+    "gisirax-tiny": _gisirax(3, 128, 4, 2, 32, 256, 512, experts=8, top=2, groups=2, keep=1, taps=3, rank=16),
+    "gisirax-0.5b": _gisirax(24, 896, 14, 2, 64, 4864, 151936),
+    "gisirax-1.5b": _gisirax(28, 1536, 12, 2, 128, 8960, 151936),
+    "gisirax-3b": _gisirax(36, 2048, 16, 2, 128, 11008, 151936),
+    "gisirax-7b": _gisirax(28, 3584, 28, 4, 128, 18944, 152064),
     "vunovik-tiny": _vunovik(3, 128, 4, 32, 64, 256, 512, taps=3),
     "vunovik-0.5b": _vunovik(24, 896, 14, 64, 64, 4864, 151936),
     "vunovik-1.5b": _vunovik(28, 1536, 12, 128, 128, 8960, 151936),

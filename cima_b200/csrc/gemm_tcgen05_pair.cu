@@ -16,6 +16,10 @@
 //
 // With the gated epilogue the tile of Q is [BN/2 gate rows | BN/2 up rows]: the leader holds the gate half,
 // the peer the up half.
+//
+// Grouped products (a routed feed-forward).  Q may hold several matrices one after another ([E][q_rows, K]); each tile
+// of 256 rows of P then belongs to one of them, named by tile_expert[row tile] (the caller lays every expert's rows
+// out from a multiple of 256 on), and a row tile marked -1 has no rows and is skipped by all three roles alike.
 #include "tcgen05.cuh"
 #include <cooperative_groups.h>
 
@@ -66,6 +70,8 @@ struct PairArgs {
   int ldo;
   int* error_flag;
   int act;                    // gated epilogue: the gate's activation (CIMA_ACT_*)
+  const int* tile_expert;     // grouped: [p_tiles] which matrix of Q a row tile multiplies with (-1: none), else null
+  int q_stride;               // grouped: rows of Q from one matrix to the next
 };
 
 // The rows a tile loads: its own 256, but the last tile of a matrix of at least 256 rows starts early enough to end
@@ -124,9 +130,11 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       int g = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
+        const int expert = a.tile_expert ? a.tile_expert[tile % p_tiles] : 0;
+        if (expert < 0) continue;
         const int p0 = tile_rows((tile % p_tiles) * (2 * BM), a.p_rows) + (int)rank * BM;
         const int qt = (tile / p_tiles) * (GATED ? QH : BN);
-        const int q0 = GATED ? (rank ? a.up_offset + qt : qt) : qt + (int)rank * QH;
+        const int q0 = (GATED ? (rank ? a.up_offset + qt : qt) : qt + (int)rank * QH) + expert * a.q_stride;
         for (int kb = 0; kb < kblocks; kb++, g++) {
           const int s = g % STAGES;
           if (g >= STAGES && !mbar_wait(&empty[s], ((g / STAGES) - 1) & 1, a.error_flag, abort_flag)) { ok = false; break; }
@@ -143,7 +151,8 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       const unsigned idesc = umma_idesc(2 * BM, BN);
       int g = 0, it = 0;
       bool ok = true;
-      for (int tile = pair; tile < n_tiles && ok; tile += pairs, it++) {
+      for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
+        if (a.tile_expert && a.tile_expert[tile % p_tiles] < 0) continue;
         const int ab = it & 1;
         if (it >= 2) ok = mbar_wait(&acc_free[ab], ((it >> 1) - 1) & 1, a.error_flag, abort_flag);
         if (!ok) break;
@@ -162,6 +171,7 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           umma_commit_pair(&empty[s]);                         // frees the stage in both blocks
         }
         if (ok) umma_commit_pair(&acc_full[ab]);               // tells both blocks' epilogues
+        it++;
       }
     }
   } else {
@@ -169,7 +179,8 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     const int quarter = warp & 3;
     const unsigned free_bar[2] = {cluster_addr(&acc_free[0], 0), cluster_addr(&acc_free[1], 0)};
     int it = 0;
-    for (int tile = pair; tile < n_tiles; tile += pairs, it++) {
+    for (int tile = pair; tile < n_tiles; tile += pairs) {
+      if (a.tile_expert && a.tile_expert[tile % p_tiles] < 0) continue;
       const int ab = it & 1;
       const int p_first = (tile % p_tiles) * (2 * BM);         // the tile's own rows start here
       const int p0 = tile_rows(p_first, a.p_rows) + (int)rank * BM;
@@ -235,6 +246,7 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(free_bar[ab]);        // 4 warps x 2 blocks arrive on the leader's barrier
+      it++;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
@@ -296,7 +308,7 @@ extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float*
   if (rc) return rc;
   rc = make_map(&mq, Q, q_rows, K, K, BN / 2);
   if (rc) return rc;
-  PairArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, error_flag, act};
+  PairArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, error_flag, act, nullptr, 0};
   switch (epi) {
     case EPI_STORE: return launch<BN, 6, EPI_STORE>(mp, mq, a, p_tiles, tiles_q, stream);
     case EPI_ACCUM: return launch<BN, 6, EPI_ACCUM>(mp, mq, a, p_tiles, tiles_q, stream);
@@ -304,4 +316,34 @@ extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float*
     case EPI_STORE_F32: return launch<BN, 6, EPI_STORE_F32>(mp, mq, a, p_tiles, tiles_q, stream);
   }
   return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: epilogue %d is not one of 0..3", epi);
+}
+
+// The grouped product: Q = [E][q_rows, K], P [p_rows, K] with p_rows a multiple of 256, tile_expert [p_rows / 256] names
+// the matrix of every row tile (-1: the tile has no rows).  Epilogues 2 (gated: a matrix of Q is [gate | up],
+// q_rows = 2 * up_offset) and 3 (float32 store); out [p_rows, ldo].
+extern "C" int cima_gemm_tcgen05_pair_grouped(const void* P, const void* Q, void* out, int epi, int p_rows, int q_rows, int E,
+                                              int K, int ldo, int up_offset, int act, const int* tile_expert,
+                                              int* error_flag, cudaStream_t stream) {
+  if (p_rows <= 0 || q_rows <= 0 || E <= 0) return 0;
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
+  if (K <= 0 || K % 8) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair_grouped: K %d must be a positive multiple of 8", K);
+  if (p_rows % (2 * BM)) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair_grouped: %d rows are not whole tiles of %d", p_rows, 2 * BM);
+  if (((uintptr_t)P | (uintptr_t)Q) & 15) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: P and Q must be 16-byte aligned");
+  if (!error_flag || !tile_expert) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: the tiles' experts and an error flag on the device are needed");
+  if (epi != EPI_SWIGLU && epi != EPI_STORE_F32) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair_grouped: epilogue %d is neither 2 (gated) nor 3 (float32)", epi);
+  if (epi == EPI_SWIGLU && (up_offset <= 0 || q_rows != 2 * up_offset)) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair_grouped: the gated epilogue needs q_rows = 2 * up_offset");
+  if ((long long)E * q_rows >= (1ll << 31)) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair_grouped: %d matrices of %d rows exceed a tensor map's coordinate", E, q_rows);
+  constexpr int BN = 256;
+  const int q_feat = epi == EPI_SWIGLU ? up_offset : q_rows;
+  const int out_cols = epi == EPI_SWIGLU ? BN / 2 : BN;
+  const int tiles_q = (q_feat + out_cols - 1) / out_cols;
+  const int p_tiles = p_rows / (2 * BM);
+  CUtensorMap mp, mq;
+  int rc = make_map(&mp, P, p_rows, K, K, BM);
+  if (rc) return rc;
+  rc = make_map(&mq, Q, (long long)E * q_rows, K, K, BN / 2);
+  if (rc) return rc;
+  PairArgs a{p_rows, q_rows, K, up_offset, nullptr, out, ldo, error_flag, act, tile_expert, q_rows};
+  if (epi == EPI_SWIGLU) return launch<BN, 6, EPI_SWIGLU>(mp, mq, a, p_tiles, tiles_q, stream);
+  return launch<BN, 6, EPI_STORE_F32>(mp, mq, a, p_tiles, tiles_q, stream);
 }

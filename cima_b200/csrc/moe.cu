@@ -7,6 +7,13 @@
 //   moe_combine   x[row] += sum_j weight[row, j] * y[row * top + j]    ascending j, float32
 // A pair's sums run over k in ascending order with one accumulator, so its result does not depend on which other
 // rows share its tile, nor on the order in which the sort placed the pairs of an expert.
+//
+// Two more roads, chosen by the caller from the step's size alone:
+//   many pairs, bfloat16   moe_sort_tiles lays every expert's pairs out from a multiple of 256 rows on and names each row
+//                          tile's expert; moe_gather_rows copies the rows of h to their places; the two products run on
+//                          the tcgen05 kernel (gemm_tcgen05_pair_grouped); moe_combine reads y through the pairs' places
+//   few pairs, bfloat16    moe_few: a warp computes one output feature for up to 8 pairs of an expert, streaming the
+//                          feature's weights with 16-byte loads (a decode step reads every touched expert once)
 #include "common.cuh"
 
 namespace {
@@ -174,14 +181,147 @@ k_moe_gemm(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __
   }
 }
 
+// pos: the row of y that holds pair (row, j), or null where y is kept by pair
 __global__ void __launch_bounds__(256)
-k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, float* __restrict__ x, int top, int H) {
+k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ pos, float* __restrict__ x,
+              int top, int H) {
   cima_pdl_wait();
   const size_t row = blockIdx.x;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float s = 0.f;
-    for (int j = 0; j < top; j++) s = fmaf(wgt[row * top + j], y[(row * top + j) * H + c], s);
+    for (int j = 0; j < top; j++) {
+      const size_t p = row * top + j;
+      s = fmaf(wgt[p], y[(pos ? (size_t)pos[p] : p) * H + c], s);
+    }
     x[row * H + c] += s;
+  }
+}
+
+// Every expert's pairs from a multiple of `tile` rows on: pos [P] the place of every pair, tile_expert [n_tiles] the
+// expert of every row tile (-1 beyond the last).  One block.
+__global__ void __launch_bounds__(1024)
+k_moe_sort_tiles(const int* __restrict__ idx, int P, int E, int tile, int n_tiles, int* __restrict__ tile_expert, int* __restrict__ pos) {
+  cima_pdl_wait();
+  __shared__ int cnt[MOE_MAX_EXPERTS];
+  __shared__ int off[MOE_MAX_EXPERTS + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int e = 0; e < E; e++) { off[e] = t; t += (cnt[e] + tile - 1) / tile; }
+    off[E] = t;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) {
+    int e = -1;
+    if (t < off[E]) {
+      int lo = 0, hi = E - 1;
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (off[mid] <= t) lo = mid; else hi = mid - 1; }
+      e = lo;
+      while (off[e + 1] <= t) e++;
+    }
+    tile_expert[t] = e;
+  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = idx[p];
+    pos[p] = off[e] * tile + atomicAdd(&cnt[e], 1);
+  }
+}
+
+// dst[pos[p]] = src[p / top]: rows of K values, 16 bytes a thread
+__global__ void __launch_bounds__(256)
+k_moe_gather_rows(const uint4* __restrict__ src, const int* __restrict__ pos, uint4* __restrict__ dst, int top, int vecs) {
+  cima_pdl_wait();
+  const size_t p = blockIdx.x;
+  const uint4* s = src + (p / top) * vecs;
+  uint4* d = dst + (size_t)pos[p] * vecs;
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) d[v] = s[v];
+}
+
+// Few pairs (a decode step).  Block (x = tile of 32 pairs of one expert as moe_sort laid them out, y = 8 output features):
+// warp w owns feature n0 + w; its lanes stride the feature's weights by 16 bytes and hold the sums of up to 8 pairs at a
+// time; a fixed shuffle tree adds the lanes.  MODE as in k_moe_gemm.
+constexpr int FEW_PAIRS = 8;
+template <int MODE>
+__global__ void __launch_bounds__(256)
+k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
+          const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ perm, int E, int top, int N,
+          int K, int act) {
+  cima_pdl_wait();
+  __shared__ int s_row[BM];
+  __shared__ int s_e, s_i0, s_n;
+  if (threadIdx.x == 0) {
+    const int tile = blockIdx.x;
+    int e = -1;
+    if (tile < tiles[E]) {
+      int lo = 0, hi = E - 1;
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (tiles[mid] <= tile) lo = mid; else hi = mid - 1; }
+      e = lo;
+      while (tiles[e + 1] <= tile) e++;
+      s_i0 = offsets[e] + (tile - tiles[e]) * BM;
+      s_n = min(BM, offsets[e + 1] - s_i0);
+    }
+    s_e = e;
+  }
+  __syncthreads();
+  const int e = s_e;
+  if (e < 0) return;
+  const int i0 = s_i0, nrows = s_n;
+  const int tid = (int)threadIdx.x;
+  if (tid < BM) s_row[tid] = tid < nrows ? (MODE == 0 ? perm[i0 + tid] / top : i0 + tid) : -1;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.y * 8 + warp;
+  if (n >= N) return;
+  const __nv_bfloat16* wg = W + ((size_t)e * (MODE == 0 ? 2 : 1) * N + n) * K;
+  const __nv_bfloat16* wu = wg + (size_t)N * K;
+  for (int r0 = 0; r0 < nrows; r0 += FEW_PAIRS) {
+    float acc[FEW_PAIRS], acc2[FEW_PAIRS];
+#pragma unroll
+    for (int r = 0; r < FEW_PAIRS; r++) acc[r] = acc2[r] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 g4 = *reinterpret_cast<const uint4*>(wg + k);
+      uint4 u4 = make_uint4(0u, 0u, 0u, 0u);
+      if (MODE == 0) u4 = *reinterpret_cast<const uint4*>(wu + k);
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+#pragma unroll
+      for (int r = 0; r < FEW_PAIRS; r++) {
+        if (r0 + r >= nrows) break;
+        const uint4 a4 = *reinterpret_cast<const uint4*>(A + (size_t)s_row[r0 + r] * lda + k);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a4);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const float2 av = __bfloat1622float2(ap[q]), gv = __bfloat1622float2(gp[q]);
+          acc[r] = fmaf(av.x, gv.x, acc[r]);
+          acc[r] = fmaf(av.y, gv.y, acc[r]);
+          if (MODE == 0) {
+            const float2 uv = __bfloat1622float2(up[q]);
+            acc2[r] = fmaf(av.x, uv.x, acc2[r]);
+            acc2[r] = fmaf(av.y, uv.y, acc2[r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < FEW_PAIRS; r++) {
+      for (int o = 16; o > 0; o >>= 1) {
+        acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+        if (MODE == 0) acc2[r] += __shfl_xor_sync(0xffffffffu, acc2[r], o);
+      }
+      if (lane == 0 && r0 + r < nrows) {
+        if (MODE == 0) {
+          const float gt = __bfloat162float(__float2bfloat16_rn(acc[r])), uv = __bfloat162float(__float2bfloat16_rn(acc2[r]));
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(i0 + r0 + r) * N + n] = __float2bfloat16_rn(cima_gate_act(gt, act) * uv);
+        } else {
+          reinterpret_cast<float*>(out)[(size_t)perm[i0 + r0 + r] * N + n] = acc[r];
+        }
+      }
+    }
   }
 }
 }  // namespace
@@ -224,8 +364,43 @@ extern "C" int cima_moe_gemm(const void* a, int adtype, int lda, const void* w, 
   return rc ? rc : cima_launch_result();
 }
 
-extern "C" int cima_moe_combine(const float* y, const float* wgt, float* x, int T, int top, int H, cudaStream_t stream) {
+// y [pairs or places, H] float32; pos [T * top] the row of y of every pair, or null where y is kept by pair
+extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos, float* x, int T, int top, int H, cudaStream_t stream) {
   if (T <= 0) return 0;
-  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, x, top, H);
+  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H);
+  return rc ? rc : cima_launch_result();
+}
+
+// tile_expert [n_tiles] and pos [P] as k_moe_sort_tiles describes; n_tiles >= ceil(P / tile) + E holds every layout.
+extern "C" int cima_moe_sort_tiles(const int* idx, int P, int E, int tile, int n_tiles, int* tile_expert, int* pos, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_EXPERTS || tile <= 0 || n_tiles < (P + tile - 1) / tile)
+    return cima_fail(CIMA_E_SIZE, "moe_sort_tiles: %d experts (at most %d), tiles of %d rows, %d tiles for %d pairs", E, MOE_MAX_EXPERTS, tile, n_tiles, P);
+  int rc = cima_launch(k_moe_sort_tiles, dim3(1), dim3(1024), (size_t)0, stream, 1, idx, P, E, tile, n_tiles, tile_expert, pos);
+  return rc ? rc : cima_launch_result();
+}
+
+// dst[pos[p]] = src[p / top] for the P pairs: rows of `row_bytes` bytes (a multiple of 16, both 16-byte aligned)
+extern "C" int cima_moe_gather_rows(const void* src, const int* pos, void* dst, int P, int top, int row_bytes, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (row_bytes <= 0 || row_bytes % 16 || (((uintptr_t)src | (uintptr_t)dst) & 15))
+    return cima_fail(CIMA_E_ARG, "moe_gather_rows: rows of %d bytes must be multiples of 16 bytes at 16-byte aligned addresses", row_bytes);
+  int rc = cima_launch(k_moe_gather_rows, dim3(P), dim3(256), (size_t)0, stream, 1, (const uint4*)src, pos, (uint4*)dst, top, row_bytes / 16);
+  return rc ? rc : cima_launch_result();
+}
+
+// The products of moe_gemm for few pairs, bfloat16 activations and weights, K a multiple of 8, 16-byte aligned rows.
+extern "C" int cima_moe_few(const void* a, int lda, const void* w, void* out, const int* offsets, const int* tiles,
+                            const int* perm, int P, int E, int top, int N, int K, int mode, int act, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (N <= 0 || K <= 0 || K % 8 || lda % 8 || E <= 0 || top <= 0 || (((uintptr_t)a | (uintptr_t)w) & 15))
+    return cima_fail(CIMA_E_SIZE, "moe_few: K %d and the row stride %d must be multiples of 8 and the operands 16-byte aligned", K, lda);
+  if (mode != 0 && mode != 1) return cima_fail(CIMA_E_ARG, "moe_few: mode %d is neither 0 (gate | up) nor 1 (down)", mode);
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "moe_few: activation code %d is unknown", act);
+  const dim3 grid((unsigned)((P + BM - 1) / BM + E), (unsigned)((N + 7) / 8));
+  if (grid.y > 65535) return cima_fail(CIMA_E_SIZE, "moe_few: %d outputs exceed one launch", N);
+  int rc;
+  if (mode == 0) rc = cima_launch(k_moe_few<0>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act);
+  else rc = cima_launch(k_moe_few<1>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act);
   return rc ? rc : cima_launch_result();
 }

@@ -135,11 +135,18 @@ class Model:
         return (all(getattr(b, "graph_safe", False) for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)
                 and (self.depth is None or self.depth.graph_safe))
 
-    def weight_bytes(self) -> int:
-        """Bytes a decode step reads of the weights: every block, final norm and head once
-        (embedding rows excluded unless the head shares the table)."""
+    def weight_bytes(self, rows: int = 1) -> int:
+        """Bytes a decode step of ``rows`` sequences reads of the weights: every block, final norm and head once
+        (embedding rows excluded unless the head shares the table); of a routed feed-forward the experts that
+        ``rows`` tokens can reach (``extra_bytes(rows)`` of a part, beyond what one token reads)."""
+        extra = 0
+        if rows > 1:
+            for b in self.blocks:
+                ff = getattr(b, "feed_forward", None)
+                if ff is not None and hasattr(ff, "extra_bytes"):
+                    extra += ff.extra_bytes(rows)
         return (sum(b.nbytes() for b in self.blocks) + self.final_norm.nbytes() + self.head.nbytes()
-                + (self.depth.nbytes() if self.depth is not None else 0))
+                + (self.depth.nbytes() if self.depth is not None else 0) + extra)
 
     # ------------------------------------------------------------------ cache
     def make_cache(self, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = 64,

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 25
+ABI_VERSION = 26
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -85,7 +85,11 @@ _SIGNATURES = {
     "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "cima_moe_sort": [_vp, _i, _i, _vp, _vp, _vp, _vp],
     "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_moe_combine": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "cima_moe_sort_tiles": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "cima_moe_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "cima_moe_few": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_gemm_tcgen05_pair_grouped": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "cima_depth_average": [_vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp],
     "cima_latent_append": [_vp, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "cima_head_linear": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -892,7 +896,9 @@ class Kernels:
                     x: torch.Tensor, act: int = 0) -> None:
         """x[t] += sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
         gate_up [E, 2 ff, H] (an expert's gate rows, then its up rows), down [E, H, ff]; x float32 [T, H].  Four launches:
-        the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum."""
+        the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum.  The
+        products take one of three roads by the step's size and dtype alone (``MOE_TC_PAIRS``, ``MOE_FEW_PAIRS``): tcgen05
+        tiles of 256 pairs, a warp a feature for the few pairs of a decode step, or the plain tiles (any dtype and size)."""
         self._need(h, "h", None, 2); self._need(gate_up, "gate_up", None, 3); self._need(down, "down", gate_up.dtype, 3)
         self._need(idx, "idx", torch.int32, 2); self._need(wgt, "wgt", torch.float32, 2); self._need(x, "x", torch.float32, 2)
         T, H = h.shape
@@ -904,6 +910,10 @@ class Kernels:
                               f"{tuple(idx.shape)}, x {tuple(x.shape)} do not agree")
         P = T * top
         dev = h.device
+        bf16 = h.dtype is torch.bfloat16 and gate_up.dtype is torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and h.stride(0) % 8 == 0
+        if bf16 and P >= self.MOE_TC_PAIRS:
+            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act)
+        few = bf16 and P <= self.MOE_FEW_PAIRS
         meta = torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
         offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
         z = torch.empty((P, ff), dtype=h.dtype, device=dev)
@@ -913,16 +923,62 @@ class Kernels:
         if self._admit("moe_sort", P * 8):
             self._check(self.lib.cima_moe_sort(idx.data_ptr(), P, E, offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(),
                                                self._stream()), "moe_sort")
-        if self._admit("moe_gemm[gate|up]", touched * 2 * ff * H * wb + P * (H + ff) * h.element_size(), 4.0 * P * ff * H):
-            self._check(self.lib.cima_moe_gemm(h.data_ptr(), dtype_code(h.dtype), h.stride(0), gate_up.data_ptr(),
-                                               dtype_code(gate_up.dtype), z.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
-                                               perm.data_ptr(), P, E, top, ff, H, 0, act, self._stream()), "moe_gemm")
-        if self._admit("moe_gemm[down]", touched * ff * H * wb + P * (ff * h.element_size() + H * 4), 2.0 * P * ff * H):
-            self._check(self.lib.cima_moe_gemm(z.data_ptr(), dtype_code(z.dtype), ff, down.data_ptr(), dtype_code(down.dtype),
-                                               y.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(), P, E, top,
-                                               H, ff, 1, 0, self._stream()), "moe_gemm")
+        name = "moe_few" if few else "moe_gemm"
+        if self._admit(f"{name}[gate|up]", touched * 2 * ff * H * wb + P * (H + ff) * h.element_size(), 4.0 * P * ff * H):
+            if few:
+                self._check(self.lib.cima_moe_few(h.data_ptr(), h.stride(0), gate_up.data_ptr(), z.data_ptr(), offsets.data_ptr(),
+                                                  tiles.data_ptr(), perm.data_ptr(), P, E, top, ff, H, 0, act, self._stream()), "moe_few")
+            else:
+                self._check(self.lib.cima_moe_gemm(h.data_ptr(), dtype_code(h.dtype), h.stride(0), gate_up.data_ptr(),
+                                                   dtype_code(gate_up.dtype), z.data_ptr(), offsets.data_ptr(), tiles.data_ptr(),
+                                                   perm.data_ptr(), P, E, top, ff, H, 0, act, self._stream()), "moe_gemm")
+        if self._admit(f"{name}[down]", touched * ff * H * wb + P * (ff * h.element_size() + H * 4), 2.0 * P * ff * H):
+            if few:
+                self._check(self.lib.cima_moe_few(z.data_ptr(), ff, down.data_ptr(), y.data_ptr(), offsets.data_ptr(),
+                                                  tiles.data_ptr(), perm.data_ptr(), P, E, top, H, ff, 1, 0, self._stream()), "moe_few")
+            else:
+                self._check(self.lib.cima_moe_gemm(z.data_ptr(), dtype_code(z.dtype), ff, down.data_ptr(), dtype_code(down.dtype),
+                                                   y.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(), P, E, top,
+                                                   H, ff, 1, 0, self._stream()), "moe_gemm")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
-            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), x.data_ptr(), T, top, H, self._stream()), "moe_combine")
+            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), None, x.data_ptr(), T, top, H, self._stream()), "moe_combine")
+
+    MOE_TC_PAIRS = 1024      # from this many (row, choice) pairs on, bfloat16 experts run on the tcgen05 tiles of 256 pairs
+    MOE_FEW_PAIRS = 128      # up to this many, a warp computes a feature for the pairs of an expert (a decode step)
+
+    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act) -> None:
+        """Many pairs in bfloat16: every expert's pairs are laid out from a multiple of 256 rows on (the rows of h copied
+        there), so that each tile of the tcgen05 product multiplies with one expert's matrix."""
+        T, H = h.shape
+        E, ff2, _ = gate_up.shape
+        ff, top = ff2 // 2, idx.shape[1]
+        P, dev, TILE = T * top, h.device, 256
+        n_tiles = -(-P // TILE) + E
+        meta = torch.empty(n_tiles + P, dtype=torch.int32, device=dev)
+        tile_expert, pos = meta[:n_tiles], meta[n_tiles:]
+        hs = torch.empty((n_tiles * TILE, H), dtype=h.dtype, device=dev)
+        z = torch.empty((n_tiles * TILE, ff), dtype=h.dtype, device=dev)
+        y = torch.empty((n_tiles * TILE, H), dtype=torch.float32, device=dev)
+        flag = self.error_flag(dev)
+        if not h.is_contiguous():
+            raise KernelError("moe_experts: the rows of h must be contiguous for the many-pairs road")
+        if self._admit("moe_sort_tiles", P * 8):
+            self._check(self.lib.cima_moe_sort_tiles(idx.data_ptr(), P, E, TILE, n_tiles, tile_expert.data_ptr(), pos.data_ptr(),
+                                                     self._stream()), "moe_sort_tiles")
+        if self._admit("moe_gather_rows", 2 * P * H * 2):
+            self._check(self.lib.cima_moe_gather_rows(h.data_ptr(), pos.data_ptr(), hs.data_ptr(), P, top, H * 2, self._stream()),
+                        "moe_gather_rows")
+        if self._admit("gemm_tcgen05_pair_grouped[gate|up]", E * 2 * ff * H * 2 + P * (H + ff) * 2, 4.0 * P * ff * H):
+            self._check(self.lib.cima_gemm_tcgen05_pair_grouped(hs.data_ptr(), gate_up.data_ptr(), z.data_ptr(), SK_SWIGLU,
+                                                                n_tiles * TILE, 2 * ff, E, H, ff, ff, act, tile_expert.data_ptr(),
+                                                                flag.data_ptr(), self._stream()), "gemm_tcgen05_pair_grouped")
+        if self._admit("gemm_tcgen05_pair_grouped[down]", E * ff * H * 2 + P * (ff * 2 + H * 4), 2.0 * P * ff * H):
+            self._check(self.lib.cima_gemm_tcgen05_pair_grouped(z.data_ptr(), down.data_ptr(), y.data_ptr(), SK_STORE_F32,
+                                                                n_tiles * TILE, H, E, ff, H, 0, 0, tile_expert.data_ptr(),
+                                                                flag.data_ptr(), self._stream()), "gemm_tcgen05_pair_grouped")
+        if self._admit("moe_combine", P * H * 4 + T * H * 8):
+            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), pos.data_ptr(), x.data_ptr(), T, top, H,
+                                                  self._stream()), "moe_combine")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:

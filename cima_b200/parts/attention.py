@@ -35,7 +35,8 @@ class Attention:
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"attention: {spec.n_heads} heads are not a multiple of {spec.n_kv_heads} kv heads")
         if self.padded and (spec.qkv_bias or spec.out_bias):
-            raise ValueError("attention: biases with padded heads are not implemented")
+            raise ValueError(f"attention: head_dim {self.dim} must be a multiple of 16 and equal to the value size {self.vdim} "
+                             f"where the projections have biases (heads are padded in the cache only without biases)")
         self.spec, self.layer, self.rt = spec, layer, rt
         self.position = build_position(spec.position, rt)
         self.qd = spec.n_heads * self.hd

@@ -78,6 +78,11 @@ class RoutedExperts:
         per = (self.gate_up[0].numel() + self.down[0].numel()) * self.gate_up.element_size()
         return self.router.nbytes() + self.top * per
 
+    def extra_bytes(self, rows: int) -> int:
+        """What a step of ``rows`` tokens reads beyond ``nbytes()`` when every token chooses other experts."""
+        per = (self.gate_up[0].numel() + self.down[0].numel()) * self.gate_up.element_size()
+        return (min(self.E, rows * self.top) - self.top) * per
+
     def scratch_row(self) -> int:
         return self.top * (2 * self.spec.intermediate + 2 * self.spec.hidden) + self.E
 

@@ -252,8 +252,9 @@ def plain_forward(cfg: dict, weights: dict, ids, return_layers: bool = False):
         x = x + m * norm(p + "norm1b", y)
         if layer.get("mlp") is not None:
             r = layer["mlp"]["router"]
-            y = plain_moe(norm(p + "norm2", x), _sub(weights, p + "mlp."), r["experts"], r["top"], r["groups"]["count"],
-                          r["groups"]["keep"], r["scale"])
+            groups = r.get("groups") or {"count": 1, "keep": 1}
+            y = plain_moe(norm(p + "norm2", x), _sub(weights, p + "mlp."), r["experts"], r["top"], groups["count"],
+                          groups["keep"], r.get("scale", 1.0))
             x = x + m * norm(p + "norm2b", y)
         streams.append(x)
     logits = norm("final.norm", x) @ weights["head"].T

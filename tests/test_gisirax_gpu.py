@@ -242,9 +242,11 @@ def test_router_choice_and_weights(E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,H,ff,E,top", [(1, 40, 24, 3, 3), (5, 96, 40, 8, 2), (200, 64, 56, 6, 1), (70, 100, 33, 10, 4)])
+@pytest.mark.parametrize("T,H,ff,E,top", [(1, 40, 24, 3, 3), (5, 96, 40, 8, 2), (200, 64, 56, 6, 1), (70, 100, 33, 10, 4),
+                                          (1100, 64, 56, 6, 1), (600, 128, 200, 5, 2), (30, 256, 64, 4, 4)])
 def test_experts_in_tiles_of_one_expert(T, H, ff, E, top, dtype):
-    """Rows spread unevenly over the experts (one expert gets none, one gets most): every tile is one expert's."""
+    """Rows spread unevenly over the experts (one expert gets none, one gets most): every tile is one expert's.  The sizes
+    reach all three roads of the products: a warp a feature (few pairs), plain tiles, and tensor-core tiles of 256 pairs."""
     g = torch.Generator().manual_seed(T * E)
     h = torch.randn(T, H, generator=g).to(DT[dtype])
     gu, dn = (torch.randn(E, 2 * ff, H, generator=g) * H ** -0.5).to(DT[dtype]), (torch.randn(E, H, ff, generator=g) * ff ** -0.5).to(DT[dtype])
@@ -391,7 +393,7 @@ def agrees(got, want, dtype, what=""):
     if dtype == "float32":
         assert e.max() < TOL[dtype], (what, float(e.max()))
     else:
-        assert e.median() < TOL[dtype] / 3 and (e > TOL[dtype]).float().mean() <= 0.08, (what, float(e.median()), float(e.max()))
+        assert e.median() < TOL[dtype] / 2 and (e > TOL[dtype]).float().mean() <= 0.08, (what, float(e.median()), float(e.max()))
 
 
 LENGTHS = {"A": 150, "B": 131, "C": 330}
