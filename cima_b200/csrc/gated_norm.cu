@@ -30,6 +30,31 @@ k_group_rmsnorm_gate(const float* __restrict__ o, const float* __restrict__ w, c
   }
 }
 
+// The same for long groups (a whole row of some thousand values): a block a (row, group).
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(256)
+k_group_rmsnorm_gate_wide(const float* __restrict__ o, const float* __restrict__ w, const TG* __restrict__ gate, int ldg,
+                          TO* __restrict__ out, int groups, int n, int shared_w, float eps) {
+  cima_pdl_wait();
+  __shared__ float red[32];
+  const long long unit = blockIdx.x;
+  const long long row = unit / groups;
+  const int grp = (int)(unit - row * groups);
+  const float* src = o + ((size_t)row * groups + grp) * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+  ss = cima_block_sum(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)n + eps);
+  const float* wp = w + (shared_w ? 0 : (size_t)grp * n);
+  const TG* gp = gate ? gate + (size_t)row * ldg + (size_t)grp * n : nullptr;
+  TO* dst = out + ((size_t)row * groups + grp) * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float y = src[i] * r * wp[i];
+    if (gp) y *= 1.0f / (1.0f + expf(-cima_to_f32<TG>(gp[i])));
+    dst[i] = cima_from_f32<TO>(y);
+  }
+}
+
 struct Branches { const float* y[4]; const float* w[4]; int n; };
 
 __global__ void __launch_bounds__(256)
@@ -62,6 +87,12 @@ extern "C" int cima_group_rmsnorm_gate(const float* o, const float* w, const voi
   const long long units = (long long)T * groups;
   const dim3 grid((unsigned)((units + 3) / 4));
   int rc;
+  if (n >= 512 && units < 0x7fffffffll) {
+    if (dtype == CIMA_F32) rc = cima_launch(k_group_rmsnorm_gate_wide<float, float>, dim3((unsigned)units), dim3(256), (size_t)0, stream, 1, o, w, (const float*)gate, ldg, (float*)out, groups, n, shared_w, eps);
+    else if (dtype == CIMA_BF16) rc = cima_launch(k_group_rmsnorm_gate_wide<__nv_bfloat16, __nv_bfloat16>, dim3((unsigned)units), dim3(256), (size_t)0, stream, 1, o, w, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, groups, n, shared_w, eps);
+    else return cima_fail(CIMA_E_DTYPE, "group_rmsnorm_gate: dtype code %d is neither float32 nor bfloat16", dtype);
+    return rc ? rc : cima_launch_result();
+  }
   if (dtype == CIMA_F32) rc = cima_launch(k_group_rmsnorm_gate<float, float>, grid, dim3(128), (size_t)0, stream, 1, o, w, (const float*)gate, ldg, (float*)out, units, groups, n, shared_w, eps);
   else if (dtype == CIMA_BF16) rc = cima_launch(k_group_rmsnorm_gate<__nv_bfloat16, __nv_bfloat16>, grid, dim3(128), (size_t)0, stream, 1, o, w, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, units, groups, n, shared_w, eps);
   else return cima_fail(CIMA_E_DTYPE, "group_rmsnorm_gate: dtype code %d is neither float32 nor bfloat16", dtype);

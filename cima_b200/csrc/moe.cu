@@ -20,14 +20,19 @@ namespace {
 constexpr int MOE_MAX_EXPERTS = 1024;
 constexpr int BM = 32, BN = 64, BK = 16;
 
-__global__ void __launch_bounds__(128)
+// One thread a row.  With at most ROUTE_SMEM_EXPERTS experts the row's scores live in shared memory (a decode step's
+// few rows would otherwise walk dependent loads from global memory); with more they stay in the caller's buffer.
+constexpr int ROUTE_THREADS = 64, ROUTE_SMEM_EXPERTS = 128;
+__global__ void __launch_bounds__(ROUTE_THREADS)
 k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int keep, float scale, int* __restrict__ idx,
             float* __restrict__ wgt) {
   cima_pdl_wait();
+  __shared__ float local[ROUTE_THREADS * (ROUTE_SMEM_EXPERTS + 1)];
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= T) return;
-  float* s = scores + (size_t)row * E;
-  for (int e = 0; e < E; e++) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  float* s = E <= ROUTE_SMEM_EXPERTS ? local + threadIdx.x * (E + 1) : scores + (size_t)row * E;
+  const float* z = scores + (size_t)row * E;
+  for (int e = 0; e < E; e++) s[e] = 1.0f / (1.0f + expf(-z[e]));
   const int per = E / groups;
   unsigned long long kept = ~0ull;
   if (keep < groups) {
@@ -333,7 +338,7 @@ extern "C" int cima_moe_route(float* scores, int T, int E, int top, int groups, 
   if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || groups > 64 || E % groups || keep <= 0 || keep > groups)
     return cima_fail(CIMA_E_SIZE, "moe_route: %d experts in %d groups of which %d stay are not accepted (at most %d experts in at most 64 equal groups)", E, groups, keep, MOE_MAX_EXPERTS);
   if (top <= 0 || top > keep * (E / groups)) return cima_fail(CIMA_E_SIZE, "moe_route: %d choices among %d experts that stay", top, keep * (E / groups));
-  int rc = cima_launch(k_moe_route, dim3((T + 127) / 128), dim3(128), (size_t)0, stream, 1, scores, T, E, top, groups, keep, scale, idx, wgt);
+  int rc = cima_launch(k_moe_route, dim3((T + ROUTE_THREADS - 1) / ROUTE_THREADS), dim3(ROUTE_THREADS), (size_t)0, stream, 1, scores, T, E, top, groups, keep, scale, idx, wgt);
   return rc ? rc : cima_launch_result();
 }
 

@@ -5,45 +5,66 @@
 //   delta rule   S <- diag(g_t) S;  u = beta_t (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                g_t one decay a key channel and token, beta_t one scalar a token; the read-out sees the token's write
 //
-// One thread owns one value channel (a column of S, `dim` registers, padded to DIMP with rows that stay zero), a block
-// 32 or 64 neighbouring columns of one (sequence, head); the step's tokens are walked in order, eight at a time through
-// shared memory (k, q, g of the head, the same for every column).  Sums over the key channels run in ascending order in
-// four interleaved partial sums, whatever the step: a token's result has the same bits whether its sequence came whole,
-// in pieces or one token at a time, alone or in a batch.  Everything is float32 but the loads of q, k, v.
+// A block owns 32 neighbouring value channels (columns of S) of one (sequence, head); a column is shared by 8 lanes of a
+// warp, each of which keeps an eighth of the column's rows in registers (rows 32 ii + 4 rg + e of row group rg, so that the
+// lanes' 16-byte reads of k, q and g from shared memory cover 32 consecutive words).  The step's tokens are walked in
+// order, 16 (8 for key sizes above 128) at a time: their k, q, g, v and beta are staged in shared memory, and the outputs
+// leave through it in whole rows.  A sum over the key channels is a lane's own rows in ascending order in two interleaved
+// partial sums, then a fixed shuffle tree over the 8 lanes, whatever the step: a token's result has the same bits whether
+// its sequence came whole, in pieces or one token at a time, alone or in a batch.  Everything is float32 but the loads of
+// q, k, v.
 #include "common.cuh"
 
 namespace {
-constexpr int REC_CHUNK = 8;
+constexpr int REC_SPLIT = 8;          // lanes that share a column
+constexpr int REC_COLS = 32;          // columns of a block: 8 warps x 4
+constexpr int REC_THREADS = 256;
 
 __device__ __forceinline__ float rec_silu(float z) { return z / (1.0f + expf(-z)); }
 
+__device__ __forceinline__ float rec_sum_over_lanes(float v) {        // over the 8 lanes of a column: lanes l, l ^ 4, l ^ 8, l ^ 16, ...
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  v += __shfl_xor_sync(0xffffffffu, v, 16);
+  return v;
+}
+
 template <typename TQ, typename TV, int DIMP, bool DELTA>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(REC_THREADS)
 k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
              const float* __restrict__ g, const float* __restrict__ beta, const float* __restrict__ decay,
              float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
              float* __restrict__ out, int heads, int kv_heads, int dim, int vdim) {
   cima_pdl_wait();
-  __shared__ __align__(16) float sk[REC_CHUNK][DIMP];
-  __shared__ __align__(16) float sq[REC_CHUNK][DIMP];
-  __shared__ __align__(16) float sg[DELTA ? REC_CHUNK : 1][DIMP];
-  __shared__ float sb[REC_CHUNK];
-  const int seq = blockIdx.z, h = blockIdx.y;
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int RP = DIMP / REC_SPLIT;                  // rows of a column that one lane keeps
+  constexpr int CH = DIMP > 128 ? 8 : 16;               // tokens staged at a time
+  __shared__ __align__(16) float sk[CH][DIMP];
+  __shared__ __align__(16) float sq[CH][DIMP];
+  __shared__ __align__(16) float sg[DELTA ? CH : 1][DIMP];
+  __shared__ float sv[CH][REC_COLS];
+  __shared__ float so[CH][REC_COLS];
+  __shared__ float sb[CH];
+  const int seq = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * REC_COLS;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rg = lane >> 2, lc = warp * 4 + (lane & 3);  // row group, column among the block's
+  const int col = col0 + lc;
   const bool live = col < vdim;
   const int kvh = h / (heads / kv_heads);
   const int first = seq_first_row[seq], n = seq_first_row[seq + 1] - first;
   float* st = state + (((size_t)seq_slot[seq] * heads + h) * dim) * (size_t)vdim + col;
-  float S[DIMP];
+  float S[RP];
 #pragma unroll
-  for (int i = 0; i < DIMP; i++) S[i] = (live && i < dim) ? st[(size_t)i * vdim] : 0.f;
+  for (int j = 0; j < RP; j++) {
+    const int row = (j >> 2) * 32 + rg * 4 + (j & 3);
+    S[j] = (live && row < dim) ? st[(size_t)row * vdim] : 0.f;
+  }
   const float dh = DELTA ? 1.f : decay[h];
   const int ldo = heads * vdim;
 
-  for (int t0 = 0; t0 < n; t0 += REC_CHUNK) {
-    const int nt = min(REC_CHUNK, n - t0);
+  for (int t0 = 0; t0 < n; t0 += CH) {
+    const int nt = min(CH, n - t0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * DIMP; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < nt * DIMP; idx += REC_THREADS) {
       const int tt = idx / DIMP, i = idx - tt * DIMP;
       const size_t row = (size_t)(first + t0 + tt);
       float kv_ = 0.f, qv = 0.f, gv = 1.f;
@@ -57,46 +78,61 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
       sq[tt][i] = qv;
       if (DELTA) sg[tt][i] = gv;
     }
+    for (int idx = threadIdx.x; idx < nt * REC_COLS; idx += REC_THREADS) {
+      const int tt = idx / REC_COLS, cc = idx - tt * REC_COLS;
+      float vv = 0.f;
+      if (col0 + cc < vdim) {
+        vv = cima_to_f32<TV>(v[(size_t)(first + t0 + tt) * ldv + (size_t)h * vdim + col0 + cc]);
+        if (!DELTA) vv = rec_silu(vv);
+      }
+      sv[tt][cc] = vv;
+    }
     if (DELTA && threadIdx.x < nt) sb[threadIdx.x] = beta[(size_t)(first + t0 + threadIdx.x) * heads + h];
     __syncthreads();
     for (int tt = 0; tt < nt; tt++) {
-      const size_t row = (size_t)(first + t0 + tt);
-      float vv = live ? cima_to_f32<TV>(v[row * ldv + (size_t)h * vdim + col]) : 0.f;
-      float u;
+      float u = sv[tt][lc];
       if (DELTA) {
-        float p[4] = {0.f, 0.f, 0.f, 0.f};
+        float p0 = 0.f, p1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DIMP; i += 4) {
+        for (int j = 0; j < RP; j += 4) {
+          const int i = (j >> 2) * 32 + rg * 4;
           const float4 g4 = *reinterpret_cast<const float4*>(&sg[tt][i]);
           const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
-          S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
-          p[0] = fmaf(S[i], k4.x, p[0]); p[1] = fmaf(S[i + 1], k4.y, p[1]);
-          p[2] = fmaf(S[i + 2], k4.z, p[2]); p[3] = fmaf(S[i + 3], k4.w, p[3]);
+          S[j] *= g4.x; S[j + 1] *= g4.y; S[j + 2] *= g4.z; S[j + 3] *= g4.w;
+          p0 = fmaf(S[j], k4.x, p0); p1 = fmaf(S[j + 1], k4.y, p1);
+          p0 = fmaf(S[j + 2], k4.z, p0); p1 = fmaf(S[j + 3], k4.w, p1);
         }
-        u = sb[tt] * (vv - ((p[0] + p[1]) + (p[2] + p[3])));
+        u = sb[tt] * (u - rec_sum_over_lanes(p0 + p1));
       } else {
-        vv = rec_silu(vv);
 #pragma unroll
-        for (int i = 0; i < DIMP; i++) S[i] *= dh;
-        u = vv;
+        for (int j = 0; j < RP; j++) S[j] *= dh;
       }
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
+      float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DIMP; i += 4) {
+      for (int j = 0; j < RP; j += 4) {
+        const int i = (j >> 2) * 32 + rg * 4;
         const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
         const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][i]);
-        S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
-        S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
-        o[0] = fmaf(S[i], q4.x, o[0]); o[1] = fmaf(S[i + 1], q4.y, o[1]);
-        o[2] = fmaf(S[i + 2], q4.z, o[2]); o[3] = fmaf(S[i + 3], q4.w, o[3]);
+        S[j] = fmaf(k4.x, u, S[j]); S[j + 1] = fmaf(k4.y, u, S[j + 1]);
+        S[j + 2] = fmaf(k4.z, u, S[j + 2]); S[j + 3] = fmaf(k4.w, u, S[j + 3]);
+        o0 = fmaf(S[j], q4.x, o0); o1 = fmaf(S[j + 1], q4.y, o1);
+        o0 = fmaf(S[j + 2], q4.z, o0); o1 = fmaf(S[j + 3], q4.w, o1);
       }
-      if (live) out[row * ldo + (size_t)h * vdim + col] = (o[0] + o[1]) + (o[2] + o[3]);
+      const float o = rec_sum_over_lanes(o0 + o1);
+      if (rg == 0) so[tt][lc] = o;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * REC_COLS; idx += REC_THREADS) {
+      const int tt = idx / REC_COLS, cc = idx - tt * REC_COLS;
+      if (col0 + cc < vdim) out[(size_t)(first + t0 + tt) * ldo + (size_t)h * vdim + col0 + cc] = so[tt][cc];
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DIMP; i++)
-      if (i < dim) st[(size_t)i * vdim] = S[i];
+    for (int j = 0; j < RP; j++) {
+      const int row = (j >> 2) * 32 + rg * 4 + (j & 3);
+      if (row < dim) st[(size_t)row * vdim] = S[j];
+    }
   }
 }
 
@@ -104,9 +140,8 @@ template <typename TQ, typename TV, bool DELTA>
 int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* g, const float* beta,
                       const float* decay, float* state, const int* seq_slot, const int* seq_first_row, float* out,
                       int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
-  const int threads = vdim > 32 ? 64 : 32;
-  const dim3 grid((vdim + threads - 1) / threads, heads, n_seqs);
-#define RUN(D) return cima_launch(k_recurrence<TQ, TV, D, DELTA>, grid, dim3(threads), (size_t)0, stream, 1, (const TQ*)q, ldq, (const TQ*)k, ldk, \
+  const dim3 grid((vdim + REC_COLS - 1) / REC_COLS, heads, n_seqs);
+#define RUN(D) return cima_launch(k_recurrence<TQ, TV, D, DELTA>, grid, dim3(REC_THREADS), (size_t)0, stream, 1, (const TQ*)q, ldq, (const TQ*)k, ldk, \
                                   (const TV*)v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, heads, kv_heads, dim, vdim)
   if (dim <= 32) RUN(32);
   if (dim <= 64) RUN(64);
