@@ -58,7 +58,7 @@ k_group_rmsnorm_gate_wide(const float* __restrict__ o, const float* __restrict__
 struct Branches { const float* y[4]; const float* w[4]; int n; };
 
 __global__ void __launch_bounds__(256)
-k_rms_mean(Branches br, float* __restrict__ x, int H, float eps) {
+k_rms_mean(Branches br, float* __restrict__ x, int H, float eps, int assign) {
   cima_pdl_wait();
   __shared__ float red[32];
   const size_t row = blockIdx.x;
@@ -74,7 +74,7 @@ k_rms_mean(Branches br, float* __restrict__ x, int H, float eps) {
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float s = 0.f;
     for (int b = 0; b < br.n; b++) s += br.y[b][row * H + c] * r[b] * br.w[b][c];
-    x[row * H + c] += s * inv;
+    x[row * H + c] = assign ? s * inv : x[row * H + c] + s * inv;
   }
 }
 }  // namespace
@@ -99,14 +99,14 @@ extern "C" int cima_group_rmsnorm_gate(const float* o, const float* w, const voi
   return rc ? rc : cima_launch_result();
 }
 
-// ys / ws: n_branches pointers to float32 [T, H] and [H]; x [T, H] float32 is added to.
+// ys / ws: n_branches pointers to float32 [T, H] and [H]; x [T, H] float32 is added to, or with assign != 0 written.
 extern "C" int cima_rms_mean(const float* const* ys, const float* const* ws, int n_branches, float* x, int T, int H, float eps,
-                             cudaStream_t stream) {
+                             int assign, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n_branches < 1 || n_branches > 4 || H <= 0) return cima_fail(CIMA_E_SIZE, "rms_mean: %d branches (1..4) of width %d", n_branches, H);
   Branches br{};
   br.n = n_branches;
   for (int b = 0; b < n_branches; b++) { br.y[b] = ys[b]; br.w[b] = ws[b]; }
-  int rc = cima_launch(k_rms_mean, dim3(T), dim3(256), (size_t)0, stream, 1, br, x, H, eps);
+  int rc = cima_launch(k_rms_mean, dim3(T), dim3(256), (size_t)0, stream, 1, br, x, H, eps, assign);
   return rc ? rc : cima_launch_result();
 }

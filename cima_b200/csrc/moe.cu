@@ -189,7 +189,7 @@ k_moe_gemm(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __
 // pos: the row of y that holds pair (row, j), or null where y is kept by pair
 __global__ void __launch_bounds__(256)
 k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ pos, float* __restrict__ x,
-              int top, int H) {
+              int top, int H, int assign) {
   cima_pdl_wait();
   const size_t row = blockIdx.x;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
@@ -198,7 +198,7 @@ k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const 
       const size_t p = row * top + j;
       s = fmaf(wgt[p], y[(pos ? (size_t)pos[p] : p) * H + c], s);
     }
-    x[row * H + c] += s;
+    x[row * H + c] = assign ? s : x[row * H + c] + s;
   }
 }
 
@@ -370,9 +370,9 @@ extern "C" int cima_moe_gemm(const void* a, int adtype, int lda, const void* w, 
 }
 
 // y [pairs or places, H] float32; pos [T * top] the row of y of every pair, or null where y is kept by pair
-extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos, float* x, int T, int top, int H, cudaStream_t stream) {
+extern "C" int cima_moe_combine(const float* y, const float* wgt, const int* pos, float* x, int T, int top, int H, int assign, cudaStream_t stream) {
   if (T <= 0) return 0;
-  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H);
+  int rc = cima_launch(k_moe_combine, dim3(T), dim3(256), (size_t)0, stream, 1, y, wgt, pos, x, top, H, assign);
   return rc ? rc : cima_launch_result();
 }
 

@@ -29,7 +29,10 @@ __device__ __forceinline__ float rec_sum_over_lanes(float v) {        // over th
   return v;
 }
 
-template <typename TQ, typename TV, int DIMP, bool DELTA>
+// CPT: columns a thread owns (its columns stand 32 apart).  With two, every read of k, q and g from shared memory serves
+// both, but a block covers 64 columns and a sequence gets half as many blocks: measured slower for one prompt (1.2 ms
+// against 0.97 ms a layer of 2,048 tokens at key and value size 128), so the launch takes one.
+template <typename TQ, typename TV, int DIMP, bool DELTA, int CPT>
 __global__ void __launch_bounds__(REC_THREADS)
 k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
              const float* __restrict__ g, const float* __restrict__ beta, const float* __restrict__ decay,
@@ -38,116 +41,158 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
   cima_pdl_wait();
   constexpr int RP = DIMP / REC_SPLIT;                  // rows of a column that one lane keeps
   constexpr int CH = DIMP > 128 ? 8 : 16;               // tokens staged at a time
+  constexpr int COLS = REC_COLS * CPT;                  // columns of the block
   __shared__ __align__(16) float sk[CH][DIMP];
   __shared__ __align__(16) float sq[CH][DIMP];
   __shared__ __align__(16) float sg[DELTA ? CH : 1][DIMP];
-  __shared__ float sv[CH][REC_COLS];
-  __shared__ float so[CH][REC_COLS];
+  __shared__ float sv[CH][COLS];
+  __shared__ float so[CH][COLS];
   __shared__ float sb[CH];
-  const int seq = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * REC_COLS;
+  const int seq = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * COLS;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int rg = lane >> 2, lc = warp * 4 + (lane & 3);  // row group, column among the block's
-  const int col = col0 + lc;
-  const bool live = col < vdim;
+  const int rg = lane >> 2, lc = warp * 4 + (lane & 3);  // row group; the thread's columns are col0 + lc + 32 x
   const int kvh = h / (heads / kv_heads);
   const int first = seq_first_row[seq], n = seq_first_row[seq + 1] - first;
-  float* st = state + (((size_t)seq_slot[seq] * heads + h) * dim) * (size_t)vdim + col;
-  float S[RP];
+  float* st = state + (((size_t)seq_slot[seq] * heads + h) * dim) * (size_t)vdim + col0 + lc;
+  float S[CPT][RP];
 #pragma unroll
-  for (int j = 0; j < RP; j++) {
-    const int row = (j >> 2) * 32 + rg * 4 + (j & 3);
-    S[j] = (live && row < dim) ? st[(size_t)row * vdim] : 0.f;
-  }
+  for (int x = 0; x < CPT; x++)
+#pragma unroll
+    for (int j = 0; j < RP; j++) {
+      const int row = (j >> 2) * 32 + rg * 4 + (j & 3);
+      S[x][j] = (col0 + lc + 32 * x < vdim && row < dim) ? st[(size_t)row * vdim + 32 * x] : 0.f;
+    }
   const float dh = DELTA ? 1.f : decay[h];
   const int ldo = heads * vdim;
+
+  // The next tokens' k, q, g, v and beta travel from global memory into registers while the current ones are worked on
+  // from shared memory: every load of a stage is issued before any of them is waited for.
+  constexpr int NLD = CH * DIMP / REC_THREADS;          // values of k (and of q, of g) a thread stages
+  constexpr int NLV = (CH * COLS + REC_THREADS - 1) / REC_THREADS;
+  float rk[NLD], rq[NLD], rgt[DELTA ? NLD : 1], rv[NLV], rb = 0.f;
+  auto fetch = [&](int t0) {
+    const int nt = min(CH, n - t0);
+#pragma unroll
+    for (int r = 0; r < NLD; r++) {
+      const int idx = threadIdx.x + r * REC_THREADS;
+      const int tt = idx / DIMP, i = idx - tt * DIMP;
+      const size_t row = (size_t)(first + t0 + tt);
+      const bool ok = tt < nt && i < dim;
+      rk[r] = ok ? cima_to_f32<TQ>(k[row * ldk + (size_t)kvh * dim + i]) : 0.f;
+      rq[r] = ok ? cima_to_f32<TQ>(q[row * ldq + (size_t)kvh * dim + i]) : 0.f;
+      if (DELTA) rgt[r] = ok ? g[(row * heads + h) * dim + i] : 1.f;
+    }
+#pragma unroll
+    for (int r = 0; r < NLV; r++) {
+      const int idx = threadIdx.x + r * REC_THREADS;
+      const int tt = idx / COLS, cc = idx - tt * COLS;
+      rv[r] = (tt < nt && col0 + cc < vdim) ? cima_to_f32<TV>(v[(size_t)(first + t0 + tt) * ldv + (size_t)h * vdim + col0 + cc]) : 0.f;
+    }
+    if (DELTA) rb = (int)threadIdx.x < nt ? beta[(size_t)(first + t0 + threadIdx.x) * heads + h] : 0.f;
+  };
+  if (n > 0) fetch(0);
 
   for (int t0 = 0; t0 < n; t0 += CH) {
     const int nt = min(CH, n - t0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * DIMP; idx += REC_THREADS) {
+#pragma unroll
+    for (int r = 0; r < NLD; r++) {
+      const int idx = threadIdx.x + r * REC_THREADS;
       const int tt = idx / DIMP, i = idx - tt * DIMP;
-      const size_t row = (size_t)(first + t0 + tt);
-      float kv_ = 0.f, qv = 0.f, gv = 1.f;
-      if (i < dim) {
-        kv_ = cima_to_f32<TQ>(k[row * ldk + (size_t)kvh * dim + i]);
-        qv = cima_to_f32<TQ>(q[row * ldq + (size_t)kvh * dim + i]);
-        if (!DELTA) { kv_ = rec_silu(kv_); qv = rec_silu(qv); }
-        if (DELTA) gv = g[(row * heads + h) * dim + i];
-      }
-      sk[tt][i] = kv_;
-      sq[tt][i] = qv;
-      if (DELTA) sg[tt][i] = gv;
+      sk[tt][i] = DELTA ? rk[r] : rec_silu(rk[r]);
+      sq[tt][i] = DELTA ? rq[r] : rec_silu(rq[r]);
+      if (DELTA) sg[tt][i] = rgt[r];
     }
-    for (int idx = threadIdx.x; idx < nt * REC_COLS; idx += REC_THREADS) {
-      const int tt = idx / REC_COLS, cc = idx - tt * REC_COLS;
-      float vv = 0.f;
-      if (col0 + cc < vdim) {
-        vv = cima_to_f32<TV>(v[(size_t)(first + t0 + tt) * ldv + (size_t)h * vdim + col0 + cc]);
-        if (!DELTA) vv = rec_silu(vv);
-      }
-      sv[tt][cc] = vv;
+#pragma unroll
+    for (int r = 0; r < NLV; r++) {
+      const int idx = threadIdx.x + r * REC_THREADS;
+      if (idx < CH * COLS) sv[idx / COLS][idx % COLS] = DELTA ? rv[r] : rec_silu(rv[r]);
     }
-    if (DELTA && threadIdx.x < nt) sb[threadIdx.x] = beta[(size_t)(first + t0 + threadIdx.x) * heads + h];
+    if (DELTA && threadIdx.x < CH) sb[threadIdx.x] = rb;
     __syncthreads();
+    if (t0 + CH < n) fetch(t0 + CH);
+#pragma unroll 2
     for (int tt = 0; tt < nt; tt++) {
-      float u = sv[tt][lc];
+      float u[CPT];
+#pragma unroll
+      for (int x = 0; x < CPT; x++) u[x] = sv[tt][lc + 32 * x];
       if (DELTA) {
-        float p0 = 0.f, p1 = 0.f;
+        float p0[CPT], p1[CPT];
+#pragma unroll
+        for (int x = 0; x < CPT; x++) p0[x] = p1[x] = 0.f;
 #pragma unroll
         for (int j = 0; j < RP; j += 4) {
           const int i = (j >> 2) * 32 + rg * 4;
           const float4 g4 = *reinterpret_cast<const float4*>(&sg[tt][i]);
           const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
-          S[j] *= g4.x; S[j + 1] *= g4.y; S[j + 2] *= g4.z; S[j + 3] *= g4.w;
-          p0 = fmaf(S[j], k4.x, p0); p1 = fmaf(S[j + 1], k4.y, p1);
-          p0 = fmaf(S[j + 2], k4.z, p0); p1 = fmaf(S[j + 3], k4.w, p1);
+#pragma unroll
+          for (int x = 0; x < CPT; x++) {
+            S[x][j] *= g4.x; S[x][j + 1] *= g4.y; S[x][j + 2] *= g4.z; S[x][j + 3] *= g4.w;
+            p0[x] = fmaf(S[x][j], k4.x, p0[x]); p1[x] = fmaf(S[x][j + 1], k4.y, p1[x]);
+            p0[x] = fmaf(S[x][j + 2], k4.z, p0[x]); p1[x] = fmaf(S[x][j + 3], k4.w, p1[x]);
+          }
         }
-        u = sb[tt] * (u - rec_sum_over_lanes(p0 + p1));
+        const float b = sb[tt];
+#pragma unroll
+        for (int x = 0; x < CPT; x++) u[x] = b * (u[x] - rec_sum_over_lanes(p0[x] + p1[x]));
       } else {
 #pragma unroll
-        for (int j = 0; j < RP; j++) S[j] *= dh;
+        for (int x = 0; x < CPT; x++)
+#pragma unroll
+          for (int j = 0; j < RP; j++) S[x][j] *= dh;
       }
-      float o0 = 0.f, o1 = 0.f;
+      float o0[CPT], o1[CPT];
+#pragma unroll
+      for (int x = 0; x < CPT; x++) o0[x] = o1[x] = 0.f;
 #pragma unroll
       for (int j = 0; j < RP; j += 4) {
         const int i = (j >> 2) * 32 + rg * 4;
         const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
         const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][i]);
-        S[j] = fmaf(k4.x, u, S[j]); S[j + 1] = fmaf(k4.y, u, S[j + 1]);
-        S[j + 2] = fmaf(k4.z, u, S[j + 2]); S[j + 3] = fmaf(k4.w, u, S[j + 3]);
-        o0 = fmaf(S[j], q4.x, o0); o1 = fmaf(S[j + 1], q4.y, o1);
-        o0 = fmaf(S[j + 2], q4.z, o0); o1 = fmaf(S[j + 3], q4.w, o1);
+#pragma unroll
+        for (int x = 0; x < CPT; x++) {
+          S[x][j] = fmaf(k4.x, u[x], S[x][j]); S[x][j + 1] = fmaf(k4.y, u[x], S[x][j + 1]);
+          S[x][j + 2] = fmaf(k4.z, u[x], S[x][j + 2]); S[x][j + 3] = fmaf(k4.w, u[x], S[x][j + 3]);
+          o0[x] = fmaf(S[x][j], q4.x, o0[x]); o1[x] = fmaf(S[x][j + 1], q4.y, o1[x]);
+          o0[x] = fmaf(S[x][j + 2], q4.z, o0[x]); o1[x] = fmaf(S[x][j + 3], q4.w, o1[x]);
+        }
       }
-      const float o = rec_sum_over_lanes(o0 + o1);
-      if (rg == 0) so[tt][lc] = o;
+#pragma unroll
+      for (int x = 0; x < CPT; x++) {
+        const float o = rec_sum_over_lanes(o0[x] + o1[x]);
+        if (rg == 0) so[tt][lc + 32 * x] = o;
+      }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * REC_COLS; idx += REC_THREADS) {
-      const int tt = idx / REC_COLS, cc = idx - tt * REC_COLS;
+    for (int idx = threadIdx.x; idx < nt * COLS; idx += REC_THREADS) {
+      const int tt = idx / COLS, cc = idx - tt * COLS;
       if (col0 + cc < vdim) out[(size_t)(first + t0 + tt) * ldo + (size_t)h * vdim + col0 + cc] = so[tt][cc];
     }
   }
-  if (live) {
+#pragma unroll
+  for (int x = 0; x < CPT; x++)
 #pragma unroll
     for (int j = 0; j < RP; j++) {
       const int row = (j >> 2) * 32 + rg * 4 + (j & 3);
-      if (row < dim) st[(size_t)row * vdim] = S[j];
+      if (col0 + lc + 32 * x < vdim && row < dim) st[(size_t)row * vdim + 32 * x] = S[x][j];
     }
-  }
 }
 
 template <typename TQ, typename TV, bool DELTA>
 int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* g, const float* beta,
                       const float* decay, float* state, const int* seq_slot, const int* seq_first_row, float* out,
                       int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
-  const dim3 grid((vdim + REC_COLS - 1) / REC_COLS, heads, n_seqs);
-#define RUN(D) return cima_launch(k_recurrence<TQ, TV, D, DELTA>, grid, dim3(REC_THREADS), (size_t)0, stream, 1, (const TQ*)q, ldq, (const TQ*)k, ldk, \
-                                  (const TV*)v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, heads, kv_heads, dim, vdim)
+  const int cpt = 1;      // two columns a thread (CPT 2) measured slower: half as many blocks, and the chain of a token is no shorter
+  const dim3 grid((vdim + REC_COLS * cpt - 1) / (REC_COLS * cpt), heads, n_seqs);
+#define RUN_C(D, C) return cima_launch(k_recurrence<TQ, TV, D, DELTA, C>, grid, dim3(REC_THREADS), (size_t)0, stream, 1, (const TQ*)q, ldq, (const TQ*)k, ldk, \
+                                       (const TV*)v, ldv, g, beta, decay, state, seq_slot, seq_first_row, out, heads, kv_heads, dim, vdim)
+#define RUN(D) { RUN_C(D, 1); }
   if (dim <= 32) RUN(32);
   if (dim <= 64) RUN(64);
   if (dim <= 128) RUN(128);
   RUN(256);
 #undef RUN
+#undef RUN_C
 }
 
 // Everything of the delta rule that is computed per token before the recurrence, in float32:

@@ -24,10 +24,16 @@ from .batch import StepEntry
 from .model import load_model
 
 
+PAGE = 64                  # positions of a cache page
+ROUNDING_REQUESTS = 64     # live requests whose last page may be partly filled beyond --max-tokens
+
+
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, out=sys.stdout, device="cuda:0",
            kernels=None) -> int:
     os.makedirs(out_dir, exist_ok=True)
-    model = load_model(model_dir, dtype=dtype, max_tokens=max_tokens, device=device, kernels=kernels)
+    # ``max_tokens`` counts the requests' own tokens; the cache holds each request in whole pages and gives every page
+    # a slot, so room for the last, partly filled page of up to ROUNDING_REQUESTS requests is added
+    model = load_model(model_dir, dtype=dtype, max_tokens=max_tokens + ROUNDING_REQUESTS * PAGE, device=device, kernels=kernels)
     slots: Dict[str, int] = {}
     for line in lines:
         line = line.strip()
@@ -67,7 +73,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64); sizes the cache")
+                    help="most tokens live requests hold at any time; sizes the cache (whole pages of 64 for up to 64 requests are added)")
     a = ap.parse_args(argv)
     return replay(a.model, a.dtype, a.out, a.max_tokens, sys.stdin)
 

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 26
+ABI_VERSION = 27
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -81,11 +81,11 @@ _SIGNATURES = {
     "cima_recurrence": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_delta_prepare": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cima_group_rmsnorm_gate": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
-    "cima_rms_mean": [_vp, _vp, _i, _vp, _i, _i, _f, _vp],
+    "cima_rms_mean": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _vp],
     "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "cima_moe_sort": [_vp, _i, _i, _vp, _vp, _vp, _vp],
     "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cima_moe_sort_tiles": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "cima_moe_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "cima_moe_few": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -862,8 +862,9 @@ class Kernels:
                                                      out.data_ptr(), dtype_code(out.dtype), T, groups, n, shared, eps,
                                                      self._stream()), "group_rmsnorm_gate")
 
-    def rms_mean(self, ys, ws, x: torch.Tensor, eps: float) -> None:
-        """x += mean over the branches b of  y_b / sqrt(mean(y_b^2) + eps) * w_b:  y_b float32 [T, H], w_b [H], at most 4."""
+    def rms_mean(self, ys, ws, x: torch.Tensor, eps: float, assign: bool = False) -> None:
+        """x += mean over the branches b of  y_b / sqrt(mean(y_b^2) + eps) * w_b:  y_b float32 [T, H], w_b [H], at most 4.
+        ``assign``: x = instead of x +=."""
         self._need(x, "x", torch.float32, 2)
         T, H = x.shape
         if not (1 <= len(ys) <= 4) or len(ws) != len(ys):
@@ -875,7 +876,7 @@ class Kernels:
         if not self._admit("rms_mean", T * H * 4 * (len(ys) + 2)): return
         yp = (ctypes.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
         wp = (ctypes.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
-        self._check(self.lib.cima_rms_mean(yp, wp, len(ys), x.data_ptr(), T, H, eps, self._stream()), "rms_mean")
+        self._check(self.lib.cima_rms_mean(yp, wp, len(ys), x.data_ptr(), T, H, eps, int(assign), self._stream()), "rms_mean")
 
     # ------------------------------------------------------------------ routed feed-forward
     def moe_route(self, scores: torch.Tensor, top: int, groups: int, keep: int, scale: float, idx: torch.Tensor,
@@ -893,8 +894,8 @@ class Kernels:
                                             self._stream()), "moe_route")
 
     def moe_experts(self, h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
-                    x: torch.Tensor, act: int = 0) -> None:
-        """x[t] += sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
+                    x: torch.Tensor, act: int = 0, assign: bool = False) -> None:
+        """x[t] += (with ``assign``: =) sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
         gate_up [E, 2 ff, H] (an expert's gate rows, then its up rows), down [E, H, ff]; x float32 [T, H].  Four launches:
         the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum.  The
         products take one of three roads by the step's size and dtype alone (``MOE_TC_PAIRS``, ``MOE_FEW_PAIRS``): tcgen05
@@ -912,7 +913,7 @@ class Kernels:
         dev = h.device
         bf16 = h.dtype is torch.bfloat16 and gate_up.dtype is torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and h.stride(0) % 8 == 0
         if bf16 and P >= self.MOE_TC_PAIRS:
-            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act)
+            return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act, assign)
         few = bf16 and P <= self.MOE_FEW_PAIRS
         meta = torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
         offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
@@ -941,12 +942,12 @@ class Kernels:
                                                    y.data_ptr(), offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(), P, E, top,
                                                    H, ff, 1, 0, self._stream()), "moe_gemm")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
-            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), None, x.data_ptr(), T, top, H, self._stream()), "moe_combine")
+            self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), None, x.data_ptr(), T, top, H, int(assign), self._stream()), "moe_combine")
 
     MOE_TC_PAIRS = 1024      # from this many (row, choice) pairs on, bfloat16 experts run on the tcgen05 tiles of 256 pairs
     MOE_FEW_PAIRS = 128      # up to this many, a warp computes a feature for the pairs of an expert (a decode step)
 
-    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act) -> None:
+    def _moe_experts_tc(self, h, gate_up, down, idx, wgt, x, act, assign=False) -> None:
         """Many pairs in bfloat16: every expert's pairs are laid out from a multiple of 256 rows on (the rows of h copied
         there), so that each tile of the tcgen05 product multiplies with one expert's matrix."""
         T, H = h.shape
@@ -978,7 +979,7 @@ class Kernels:
                                                                 flag.data_ptr(), self._stream()), "gemm_tcgen05_pair_grouped")
         if self._admit("moe_combine", P * H * 4 + T * H * 8):
             self._check(self.lib.cima_moe_combine(y.data_ptr(), wgt.data_ptr(), pos.data_ptr(), x.data_ptr(), T, top, H,
-                                                  self._stream()), "moe_combine")
+                                                  int(assign), self._stream()), "moe_combine")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:

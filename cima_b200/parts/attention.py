@@ -125,6 +125,13 @@ class Attention:
     takes_next_norm = True         # forward(..., next_norm=): the norm that will read x next, for its last product
 
     def forward(self, h, x: torch.Tensor, batch, cache, site: int, next_norm=None):
+        return self.out.accumulate(self._attend(h, batch, cache, site), x, next_norm)
+
+    def produce(self, h, batch, cache, site: int) -> torch.Tensor:
+        """The mixer's output as float32 rows of its own (what ``forward`` adds into x)."""
+        return self.out.logits(self._attend(h, batch, cache, site))
+
+    def _attend(self, h, batch, cache, site: int) -> torch.Tensor:
         s, K_ = self.spec, self.rt.kernels
         kv = cache.layer_kv(site)
         writes = s.cache_from is None
@@ -153,7 +160,7 @@ class Attention:
         else:
             K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, self.hd, s.scale, s.window, from_cache,
                          after_append=True)
-        return self.out.accumulate(att, x, next_norm)
+        return att
 
 
 register_mixer("attention", Attention)

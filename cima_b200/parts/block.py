@@ -179,7 +179,8 @@ class ParallelBlock:
 class SandwichBlock:
     """x += m * post1(mixer(pre1(x))), then x += m * post2(feed_forward(pre2(x))): every sublayer stands between two
     norms, and what it adds to the stream is scaled by ``residual_mult``.  A sublayer adds its output into a zeroed
-    float32 buffer (the parts' one interface: they add into the rows they are given), which the norm behind it reads;
+    float32 buffer (the parts' one interface: they add into the rows they are given) or, where it offers ``produce``,
+    hands its output over as float32 rows of its own; the norm behind it reads those;
     where that norm is a Dynamic Tanh, it, the scaled residual sum and the norm in front of the next sublayer are one
     kernel.  Any registered norm serves; one without ``tensors`` runs as separate launches."""
 
@@ -262,16 +263,22 @@ class SandwichBlock:
             h = info.h
         else:
             h = self.mixer_norm(x)
-        y = torch.zeros_like(x)
-        self.mixer.forward(h, y, batch, cache, site)
+        if hasattr(self.mixer, "produce"):
+            y = self.mixer.produce(h, batch, cache, site)
+        else:
+            y = torch.zeros_like(x)
+            self.mixer.forward(h, y, batch, cache, site)
         if self.feed_forward is None:
             h = self._close(x, y, self.mixer_post, next_norm)
             return RowsInfo(norm=next_norm, h=h) if h is not None else None
         h = self._close(x, y, self.mixer_post, self.ffn_norm)
         if h is None:
             h = self.ffn_norm(x)
-        y.zero_()
-        self.feed_forward.forward(h, y, batch)
+        if hasattr(self.feed_forward, "produce"):
+            y = self.feed_forward.produce(h, batch)
+        else:
+            y.zero_()
+            self.feed_forward.forward(h, y, batch)
         h = self._close(x, y, self.ffn_post, next_norm)
         return RowsInfo(norm=next_norm, h=h) if h is not None else None
 

@@ -80,6 +80,13 @@ class DecayAttention:
         return [StateRequest(self.state_name(site), (self.heads, self.dim, self.vdim), torch.float32)]
 
     def forward(self, h, x: torch.Tensor, batch, cache, site: int, next_norm=None):
+        return self.out.accumulate(self._gated(h, batch, cache, site), x, next_norm)
+
+    def produce(self, h, batch, cache, site: int) -> torch.Tensor:
+        """The mixer's output as float32 rows of its own (what ``forward`` adds into x)."""
+        return self.out.logits(self._gated(h, batch, cache, site))
+
+    def _gated(self, h, batch, cache, site: int) -> torch.Tensor:
         K_, rt = self.rt.kernels, self.rt
         if hasattr(h, "tensor"):
             h = h.tensor()
@@ -90,7 +97,7 @@ class DecayAttention:
                       self.heads, self.heads, self.dim, self.vdim, decay=self.decay)
         gated = rt.empty(rows, vd)
         K_.group_rmsnorm_gate(o, self.norm, p[:, 2 * qd + vd:], gated, 1, self.eps)
-        return self.out.accumulate(gated, x, next_norm)
+        return gated
 
 
 register_mixer("decay_attention", DecayAttention)

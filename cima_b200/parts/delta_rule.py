@@ -109,6 +109,13 @@ class ChannelDelta:
         return [StateRequest(self.state_name(site), (self.heads, self.dim, self.vdim), torch.float32)] + self.conv.cache_requests(site)
 
     def forward(self, h, x: torch.Tensor, batch, cache, site: int, next_norm=None):
+        return self.out.accumulate(self._gated(h, batch, cache, site), x, next_norm)
+
+    def produce(self, h, batch, cache, site: int) -> torch.Tensor:
+        """The mixer's output as float32 rows of its own (what ``forward`` adds into x)."""
+        return self.out.logits(self._gated(h, batch, cache, site))
+
+    def _gated(self, h, batch, cache, site: int) -> torch.Tensor:
         K_, rt = self.rt.kernels, self.rt
         if hasattr(h, "tensor"):
             h = h.tensor()
@@ -129,7 +136,7 @@ class ChannelDelta:
         gate = self.g2.store(self.g1.store(h))
         gated = rt.empty(rows, self.vd)
         K_.group_rmsnorm_gate(o, self.norm, gate, gated, self.heads, self.eps)
-        return self.out.accumulate(gated, x, next_norm)
+        return gated
 
 
 register_mixer("channel_delta", ChannelDelta)

@@ -89,6 +89,16 @@ class RoutedExperts:
     graph_safe = True
 
     def forward(self, h, x: torch.Tensor, batch, next_norm=None):
+        self._run(h, x, False)
+        return None
+
+    def produce(self, h, batch) -> torch.Tensor:
+        """The feed-forward's output as float32 rows of its own (what ``forward`` adds into x)."""
+        y = self.rt.empty(h.shape[0], self.spec.hidden, dtype=torch.float32)
+        self._run(h, y, True)
+        return y
+
+    def _run(self, h, x: torch.Tensor, assign: bool) -> None:
         K_, rt = self.rt.kernels, self.rt
         if hasattr(h, "tensor"):
             h = h.tensor()
@@ -97,8 +107,7 @@ class RoutedExperts:
         idx = rt.empty(rows, self.top, dtype=torch.int32)
         wgt = rt.empty(rows, self.top, dtype=torch.float32)
         K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt)
-        K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act)
-        return None
+        K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act, assign=assign)
 
 
 register_feed_forward("moe", RoutedExperts)

@@ -78,16 +78,30 @@ class SideBySide:
             raise ValueError("side_by_side: more than one branch keeps keys and values; a site has one place in the cache")
         return reqs
 
+    def _branch_outputs(self, h, like: torch.Tensor, batch, cache, site: int):
+        """Every branch's output as float32 rows of its own: from its ``produce`` where it has one, else added into zeros."""
+        ys = []
+        for b in self.branches:
+            if hasattr(b, "produce"):
+                ys.append(b.produce(h, batch, cache, site))
+            else:
+                y = torch.zeros_like(like)
+                b.forward(h, y, batch, cache, site)
+                ys.append(y)
+        return ys
+
     def forward(self, h, x: torch.Tensor, batch, cache, site: int, next_norm=None):
         if hasattr(h, "tensor"):
             h = h.tensor()
-        ys = []
-        for b in self.branches:
-            y = torch.zeros_like(x)
-            b.forward(h, y, batch, cache, site)
-            ys.append(y)
-        self.rt.kernels.rms_mean(ys, self.weights, x, self.eps)
+        self.rt.kernels.rms_mean(self._branch_outputs(h, x, batch, cache, site), self.weights, x, self.eps)
         return None
+
+    def produce(self, h, batch, cache, site: int) -> torch.Tensor:
+        if hasattr(h, "tensor"):
+            h = h.tensor()
+        y = self.rt.empty(h.shape[0], self.spec.hidden, dtype=torch.float32)
+        self.rt.kernels.rms_mean(self._branch_outputs(h, y, batch, cache, site), self.weights, y, self.eps, assign=True)
+        return y
 
 
 register_mixer("side_by_side", SideBySide)

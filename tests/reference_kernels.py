@@ -359,11 +359,14 @@ def _group_rmsnorm_gate(self, o, w, gate, out, groups, eps):
     out.copy_(z.view(T, W).to(out.dtype))
 
 
-def _rms_mean(self, ys, ws, x, eps):
+def _rms_mean(self, ys, ws, x, eps, assign=False):
     acc = torch.zeros_like(x)
     for y, w in zip(ys, ws):
         acc = acc + y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * w
-    x.add_(acc / len(ys))
+    if assign:
+        x.copy_(acc / len(ys))
+    else:
+        x.add_(acc / len(ys))
 
 
 # ---------------------------------------------------------------------- routed feed-forward
@@ -382,7 +385,7 @@ def _moe_route(self, scores, top, groups, keep, scale, idx, wgt):
     scores.copy_(s)
 
 
-def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0):
+def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0, assign=False):
     ff = gate_up.shape[1] // 2
     hf = h.float()
     for t in range(h.shape[0]):
@@ -392,7 +395,7 @@ def _moe_experts(self, h, gate_up, down, idx, wgt, x, act=0):
             gu = (gate_up[e].float() @ hf[t]).to(h.dtype).float()
             z = (self.gate_act(gu[:ff], act) * gu[ff:]).to(h.dtype).float()
             acc = acc + wgt[t, j] * (down[e].float() @ z)
-        x[t] += acc
+        x[t] = acc if assign else x[t] + acc
 
 
 for _name, _fn in (("dyt", _dyt), ("dyt_add", _dyt_add), ("embed_bigram", _embed_bigram), ("recurrence", _recurrence),
