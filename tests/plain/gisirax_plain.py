@@ -238,9 +238,12 @@ def plain_mixer(h, layer: dict, W: dict, eps: float):
 def plain_forward(cfg: dict, weights: dict, ids, return_layers: bool = False):
     """Logits [T, vocab] of one sequence (and the stream after every layer)."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
-    big = cfg["embedding"]["bigram"]
-    x = plain_embedding(ids, weights["embed"], weights["bigram"], cfg["embedding"]["scale"], big["buckets"], big["mul_prev"],
-                        big["mul_cur"])
+    big = cfg["embedding"].get("bigram")
+    if big is not None:
+        x = plain_embedding(ids, weights["embed"], weights["bigram"], cfg["embedding"]["scale"], big["buckets"], big["mul_prev"],
+                            big["mul_cur"])
+    else:
+        x = weights["embed"][torch.as_tensor(ids, dtype=torch.long)] * cfg["embedding"]["scale"]
     streams = []
 
     def norm(name, z):
