@@ -84,7 +84,7 @@ def test_random_configuration(seed, tmp_path):
         for what, got in runs.items():
             if kind == "sharp":
                 e = row_errors(got, want)
-                assert e.max() < 5e-5, (cfg, what, float(e.max()))
+                assert e.max() < 2e-4, (cfg, what, float(e.max()))      # sums of float32 through sharp softmaxes; a fault shows at 1e-2
             elif dtype == "float32":
                 exact[what] = got
             else:
