@@ -13,6 +13,7 @@ k_embed_bigram(const int* __restrict__ ids, const TW* __restrict__ table, const 
                const int* __restrict__ row_seq, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                int* __restrict__ prev_state, int one_row) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   const int row = blockIdx.x;
   const int tok = ids[row];
   const int seq = one_row ? row : row_seq[row];
@@ -37,6 +38,7 @@ k_embed_bigram(const int* __restrict__ ids, const TW* __restrict__ table, const 
 __global__ void k_bigram_state(const int* __restrict__ ids, const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                                int* __restrict__ prev_state, int n_seqs) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s < n_seqs) prev_state[seq_slot[s]] = ids[seq_first_row[s + 1] - 1];
 }

@@ -14,6 +14,7 @@ __global__ void __launch_bounds__(DYT_THREADS)
 k_dyt(const float* __restrict__ x, const float* __restrict__ alpha, const float* __restrict__ w, const float* __restrict__ b,
       TO* __restrict__ out, size_t n, int H) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   const float a = alpha[0];
   for (size_t i = (size_t)blockIdx.x * DYT_THREADS + threadIdx.x; i < n; i += (size_t)gridDim.x * DYT_THREADS) {
     const int c = (int)(i % (size_t)H);
@@ -27,6 +28,7 @@ k_dyt_add(float* __restrict__ x, const float* __restrict__ y, const float* __res
           const float* __restrict__ b1, float mult, const float* __restrict__ alpha2, const float* __restrict__ w2,
           const float* __restrict__ b2, TO* __restrict__ h, size_t n, int H) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   const float a1 = alpha1[0], a2 = w2 ? alpha2[0] : 0.f;
   for (size_t i = (size_t)blockIdx.x * DYT_THREADS + threadIdx.x; i < n; i += (size_t)gridDim.x * DYT_THREADS) {
     const int c = (int)(i % (size_t)H);

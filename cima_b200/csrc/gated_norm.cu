@@ -10,6 +10,7 @@ __global__ void __launch_bounds__(128)
 k_group_rmsnorm_gate(const float* __restrict__ o, const float* __restrict__ w, const TG* __restrict__ gate, int ldg,
                      TO* __restrict__ out, long long units, int groups, int n, int shared_w, float eps) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= units) return;
   const int lane = threadIdx.x & 31;
@@ -36,6 +37,7 @@ __global__ void __launch_bounds__(256)
 k_group_rmsnorm_gate_wide(const float* __restrict__ o, const float* __restrict__ w, const TG* __restrict__ gate, int ldg,
                           TO* __restrict__ out, int groups, int n, int shared_w, float eps) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   __shared__ float red[32];
   const long long unit = blockIdx.x;
   const long long row = unit / groups;
@@ -60,6 +62,7 @@ struct Branches { const float* y[4]; const float* w[4]; int n; };
 __global__ void __launch_bounds__(256)
 k_rms_mean(Branches br, float* __restrict__ x, int H, float eps, int assign) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // a short kernel: the next one may be set up while this one runs (it waits for this one's end itself)
   __shared__ float red[32];
   const size_t row = blockIdx.x;
   float r[4];

@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS)
 k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int keep, float scale, int* __restrict__ idx,
             float* __restrict__ wgt) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   __shared__ float local[ROUTE_THREADS * (ROUTE_SMEM_EXPERTS + 1)];
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= T) return;
@@ -75,6 +76,7 @@ k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int k
 __global__ void __launch_bounds__(1024)
 k_moe_sort(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ perm) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   __shared__ int cnt[MOE_MAX_EXPERTS];
   __shared__ int off[MOE_MAX_EXPERTS + 1];
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -191,6 +193,7 @@ __global__ void __launch_bounds__(256)
 k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ pos, float* __restrict__ x,
               int top, int H, int assign) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   const size_t row = blockIdx.x;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float s = 0.f;
@@ -207,6 +210,7 @@ k_moe_combine(const float* __restrict__ y, const float* __restrict__ wgt, const 
 __global__ void __launch_bounds__(1024)
 k_moe_sort_tiles(const int* __restrict__ idx, int P, int E, int tile, int n_tiles, int* __restrict__ tile_expert, int* __restrict__ pos) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   __shared__ int cnt[MOE_MAX_EXPERTS];
   __shared__ int off[MOE_MAX_EXPERTS + 1];
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -241,6 +245,7 @@ k_moe_sort_tiles(const int* __restrict__ idx, int P, int E, int tile, int n_tile
 __global__ void __launch_bounds__(256)
 k_moe_gather_rows(const uint4* __restrict__ src, const int* __restrict__ pos, uint4* __restrict__ dst, int top, int vecs) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   const size_t p = blockIdx.x;
   const uint4* s = src + (p / top) * vecs;
   uint4* d = dst + (size_t)pos[p] * vecs;

@@ -169,6 +169,7 @@ k_recurrence(const TQ* __restrict__ q, int ldq, const TQ* __restrict__ k, int ld
       if (col0 + cc < vdim) out[(size_t)(first + t0 + tt) * ldo + (size_t)h * vdim + col0 + cc] = so[tt][cc];
     }
   }
+  cima_pdl_trigger();        // the tokens are done: the next kernel may be set up while the state is stored
 #pragma unroll
   for (int x = 0; x < CPT; x++)
 #pragma unroll
@@ -205,6 +206,7 @@ k_delta_prepare(const TA* __restrict__ qk, int ldqk, const TA* __restrict__ a, i
                 const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ qn, float* __restrict__ kn,
                 float* __restrict__ g, float* __restrict__ beta, int heads, int kv_heads, int dim) {
   cima_pdl_wait();
+  cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   const size_t row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const float qscale = 1.0f / sqrtf((float)dim);
