@@ -20,17 +20,53 @@ namespace {
 constexpr int MOE_MAX_EXPERTS = 1024;
 constexpr int BM = 32, BN = 64, BK = 16;
 
+// The pairs of idx [P] ordered by expert, by the threads of one block (cnt, off: shared memory of MOE_MAX_EXPERTS (+ 1) ints).
+__device__ __forceinline__ void moe_sort_block(const int* idx, int P, int E, int* offsets, int* tiles, int* perm, int* cnt, int* off) {
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, t = 0;
+    for (int e = 0; e < E; e++) {
+      off[e] = o; offsets[e] = o; tiles[e] = t;
+      o += cnt[e];
+      t += (cnt[e] + BM - 1) / BM;
+    }
+    off[E] = o; offsets[E] = o; tiles[E] = t;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = idx[p];
+    perm[off[e] + atomicAdd(&cnt[e], 1)] = p;
+  }
+}
+
 // One thread a row.  With at most ROUTE_SMEM_EXPERTS experts the row's scores live in shared memory (a decode step's
 // few rows would otherwise walk dependent loads from global memory); with more they stay in the caller's buffer.
 constexpr int ROUTE_THREADS = 64, ROUTE_SMEM_EXPERTS = 128;
+__device__ __forceinline__ void moe_route_row(float* scores, float* local, int row, int E, int top, int groups, int keep, float scale,
+                                              int* idx, float* wgt);
 __global__ void __launch_bounds__(ROUTE_THREADS)
 k_moe_route(float* __restrict__ scores, int T, int E, int top, int groups, int keep, float scale, int* __restrict__ idx,
-            float* __restrict__ wgt) {
+            float* __restrict__ wgt, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ perm) {
   cima_pdl_wait();
   cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   __shared__ float local[ROUTE_THREADS * (ROUTE_SMEM_EXPERTS + 1)];
+  __shared__ int cnt[MOE_MAX_EXPERTS];
+  __shared__ int off[MOE_MAX_EXPERTS + 1];
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= T) return;
+  if (row < T) moe_route_row(scores, local, row, E, top, groups, keep, scale, idx, wgt);
+  if (offsets) {             // a step of one block's rows: the pairs are ordered by expert here, which saves moe_sort's launch
+    __syncthreads();
+    moe_sort_block(idx, T * top, E, offsets, tiles, perm, cnt, off);
+  }
+}
+
+__device__ __forceinline__ void moe_route_row(float* scores, float* local, int row, int E, int top, int groups, int keep, float scale,
+                                              int* idx, float* wgt) {
   float* s = E <= ROUTE_SMEM_EXPERTS ? local + threadIdx.x * (E + 1) : scores + (size_t)row * E;
   const float* z = scores + (size_t)row * E;
   for (int e = 0; e < E; e++) s[e] = 1.0f / (1.0f + expf(-z[e]));
@@ -79,26 +115,7 @@ k_moe_sort(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets,
   cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
   __shared__ int cnt[MOE_MAX_EXPERTS];
   __shared__ int off[MOE_MAX_EXPERTS + 1];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
-  __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int o = 0, t = 0;
-    for (int e = 0; e < E; e++) {
-      off[e] = o; offsets[e] = o; tiles[e] = t;
-      o += cnt[e];
-      t += (cnt[e] + BM - 1) / BM;
-    }
-    off[E] = o; offsets[E] = o; tiles[E] = t;
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
-  __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) {
-    const int e = idx[p];
-    perm[off[e] + atomicAdd(&cnt[e], 1)] = p;
-  }
+  moe_sort_block(idx, P, E, offsets, tiles, perm, cnt, off);
 }
 
 // MODE 0: A = h [T, K] gathered by row = perm[i] / top; W = [E, 2 N, K] (gate rows, then up rows); out z [P, N] (TA) at i.
@@ -252,10 +269,11 @@ k_moe_gather_rows(const uint4* __restrict__ src, const int* __restrict__ pos, ui
   for (int v = threadIdx.x; v < vecs; v += blockDim.x) d[v] = s[v];
 }
 
-// Few pairs (a decode step).  Block (x = tile of 32 pairs of one expert as moe_sort laid them out, y = 8 output features):
-// warp w owns feature n0 + w; its lanes stride the feature's weights by 16 bytes and hold the sums of up to 8 pairs at a
-// time; a fixed shuffle tree adds the lanes.  MODE as in k_moe_gemm.
+// Few pairs (a decode step).  Block (x = tile of 32 pairs of one expert as moe_sort laid them out, y = 8 or 16 output
+// features): warp w owns feature n0 + w (and n0 + w + 8); its lanes stride the features' weights by 16 bytes and hold the sums
+// of up to 8 pairs at a time; a fixed shuffle tree adds the lanes.  MODE as in k_moe_gemm.
 constexpr int FEW_PAIRS = 8;
+constexpr int FEW_ROWS = 2;          // rows of weights a warp streams at once (4 measured the same: 0.663 against 0.659 ms a step)
 template <int MODE>
 __global__ void __launch_bounds__(256)
 k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
@@ -285,20 +303,35 @@ k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __r
   if (tid < BM) s_row[tid] = tid < nrows ? (MODE == 0 ? perm[i0 + tid] / top : i0 + tid) : -1;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n = blockIdx.y * 8 + warp;
+  // A warp streams FEW_ROWS rows of weights at once, so that enough loads are in flight: a feature's gate and up rows
+  // (MODE 0) or the rows of features n and n + 8 (MODE 1); with four, two and four features.  With one row a warp the down
+  // product stood at 0.4 of the bandwidth (a decode step of the 1.5B shape at batch 8 took 0.72 ms, with two 0.66 ms).
+  constexpr int FEATS = MODE == 0 ? FEW_ROWS / 2 : FEW_ROWS;          // features a warp computes
+  const int n = blockIdx.y * (8 * FEATS) + warp;
   if (n >= N) return;
-  const __nv_bfloat16* wg = W + ((size_t)e * (MODE == 0 ? 2 : 1) * N + n) * K;
-  const __nv_bfloat16* wu = wg + (size_t)N * K;
-  for (int r0 = 0; r0 < nrows; r0 += FEW_PAIRS) {
-    float acc[FEW_PAIRS], acc2[FEW_PAIRS];
+  const __nv_bfloat16* wrow[FEW_ROWS];
+  bool valid[FEATS];
 #pragma unroll
-    for (int r = 0; r < FEW_PAIRS; r++) acc[r] = acc2[r] = 0.f;
+  for (int f = 0; f < FEATS; f++) {
+    valid[f] = n + 8 * f < N;
+    const int nf = valid[f] ? n + 8 * f : n;
+    if (MODE == 0) {
+      wrow[2 * f] = W + ((size_t)e * 2 * N + nf) * K;
+      wrow[2 * f + 1] = wrow[2 * f] + (size_t)N * K;
+    } else {
+      wrow[f] = W + ((size_t)e * N + nf) * K;
+    }
+  }
+  for (int r0 = 0; r0 < nrows; r0 += FEW_PAIRS) {
+    float acc[FEW_ROWS][FEW_PAIRS];
+#pragma unroll
+    for (int j = 0; j < FEW_ROWS; j++)
+#pragma unroll
+      for (int r = 0; r < FEW_PAIRS; r++) acc[j][r] = 0.f;
     for (int k = lane * 8; k < K; k += 256) {
-      const uint4 g4 = *reinterpret_cast<const uint4*>(wg + k);
-      uint4 u4 = make_uint4(0u, 0u, 0u, 0u);
-      if (MODE == 0) u4 = *reinterpret_cast<const uint4*>(wu + k);
-      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
-      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+      uint4 w4[FEW_ROWS];
+#pragma unroll
+      for (int j = 0; j < FEW_ROWS; j++) w4[j] = *reinterpret_cast<const uint4*>(wrow[j] + k);
 #pragma unroll
       for (int r = 0; r < FEW_PAIRS; r++) {
         if (r0 + r >= nrows) break;
@@ -306,29 +339,32 @@ k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __r
         const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a4);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-          const float2 av = __bfloat1622float2(ap[q]), gv = __bfloat1622float2(gp[q]);
-          acc[r] = fmaf(av.x, gv.x, acc[r]);
-          acc[r] = fmaf(av.y, gv.y, acc[r]);
-          if (MODE == 0) {
-            const float2 uv = __bfloat1622float2(up[q]);
-            acc2[r] = fmaf(av.x, uv.x, acc2[r]);
-            acc2[r] = fmaf(av.y, uv.y, acc2[r]);
+          const float2 av = __bfloat1622float2(ap[q]);
+#pragma unroll
+          for (int j = 0; j < FEW_ROWS; j++) {
+            const float2 wv = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&w4[j])[q]);
+            acc[j][r] = fmaf(av.x, wv.x, acc[j][r]);
+            acc[j][r] = fmaf(av.y, wv.y, acc[j][r]);
           }
         }
       }
     }
 #pragma unroll
     for (int r = 0; r < FEW_PAIRS; r++) {
-      for (int o = 16; o > 0; o >>= 1) {
-        acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
-        if (MODE == 0) acc2[r] += __shfl_xor_sync(0xffffffffu, acc2[r], o);
-      }
+#pragma unroll
+      for (int j = 0; j < FEW_ROWS; j++)
+        for (int o = 16; o > 0; o >>= 1) acc[j][r] += __shfl_xor_sync(0xffffffffu, acc[j][r], o);
       if (lane == 0 && r0 + r < nrows) {
-        if (MODE == 0) {
-          const float gt = __bfloat162float(__float2bfloat16_rn(acc[r])), uv = __bfloat162float(__float2bfloat16_rn(acc2[r]));
-          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(i0 + r0 + r) * N + n] = __float2bfloat16_rn(cima_gate_act(gt, act) * uv);
-        } else {
-          reinterpret_cast<float*>(out)[(size_t)perm[i0 + r0 + r] * N + n] = acc[r];
+#pragma unroll
+        for (int f = 0; f < FEATS; f++) {
+          if (!valid[f]) continue;
+          if (MODE == 0) {
+            // gate and up are rounded to bfloat16 before the activation, as stored projections would be
+            const float gt = __bfloat162float(__float2bfloat16_rn(acc[2 * f][r])), uv = __bfloat162float(__float2bfloat16_rn(acc[2 * f + 1][r]));
+            reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(i0 + r0 + r) * N + n + 8 * f] = __float2bfloat16_rn(cima_gate_act(gt, act) * uv);
+          } else {
+            reinterpret_cast<float*>(out)[(size_t)perm[i0 + r0 + r] * N + n + 8 * f] = acc[f][r];
+          }
         }
       }
     }
@@ -337,13 +373,16 @@ k_moe_few(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __r
 }  // namespace
 
 // scores [T, E] float32: the router's logits on entry, scratch afterwards.  idx [T, top] int32, wgt [T, top] float32.
+// offsets, tiles, perm: null, or (at most 64 rows) the outputs of moe_sort, made by the same launch.
 extern "C" int cima_moe_route(float* scores, int T, int E, int top, int groups, int keep, float scale, int* idx, float* wgt,
-                              cudaStream_t stream) {
+                              int* offsets, int* tiles, int* perm, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || groups > 64 || E % groups || keep <= 0 || keep > groups)
     return cima_fail(CIMA_E_SIZE, "moe_route: %d experts in %d groups of which %d stay are not accepted (at most %d experts in at most 64 equal groups)", E, groups, keep, MOE_MAX_EXPERTS);
   if (top <= 0 || top > keep * (E / groups)) return cima_fail(CIMA_E_SIZE, "moe_route: %d choices among %d experts that stay", top, keep * (E / groups));
-  int rc = cima_launch(k_moe_route, dim3((T + ROUTE_THREADS - 1) / ROUTE_THREADS), dim3(ROUTE_THREADS), (size_t)0, stream, 1, scores, T, E, top, groups, keep, scale, idx, wgt);
+  if ((offsets || tiles || perm) && (!offsets || !tiles || !perm || T > ROUTE_THREADS))
+    return cima_fail(CIMA_E_ARG, "moe_route: ordering the pairs here takes offsets, tiles and perm and at most %d rows (%d given)", ROUTE_THREADS, T);
+  int rc = cima_launch(k_moe_route, dim3((T + ROUTE_THREADS - 1) / ROUTE_THREADS), dim3(ROUTE_THREADS), (size_t)0, stream, 1, scores, T, E, top, groups, keep, scale, idx, wgt, offsets, tiles, perm);
   return rc ? rc : cima_launch_result();
 }
 
@@ -407,7 +446,8 @@ extern "C" int cima_moe_few(const void* a, int lda, const void* w, void* out, co
     return cima_fail(CIMA_E_SIZE, "moe_few: K %d and the row stride %d must be multiples of 8 and the operands 16-byte aligned", K, lda);
   if (mode != 0 && mode != 1) return cima_fail(CIMA_E_ARG, "moe_few: mode %d is neither 0 (gate | up) nor 1 (down)", mode);
   if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "moe_few: activation code %d is unknown", act);
-  const dim3 grid((unsigned)((P + BM - 1) / BM + E), (unsigned)((N + 7) / 8));
+  const int per_block = 8 * (mode == 0 ? FEW_ROWS / 2 : FEW_ROWS);          // features of a block: its 8 warps' 
+  const dim3 grid((unsigned)((P + BM - 1) / BM + E), (unsigned)((N + per_block - 1) / per_block));
   if (grid.y > 65535) return cima_fail(CIMA_E_SIZE, "moe_few: %d outputs exceed one launch", N);
   int rc;
   if (mode == 0) rc = cima_launch(k_moe_few<0>, grid, dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, out, offsets, tiles, perm, E, top, N, K, act);

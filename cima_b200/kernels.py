@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 27
+ABI_VERSION = 28
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -82,7 +82,7 @@ _SIGNATURES = {
     "cima_delta_prepare": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cima_group_rmsnorm_gate": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
     "cima_rms_mean": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _vp],
-    "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
+    "cima_moe_route": [_vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp],
     "cima_moe_sort": [_vp, _i, _i, _vp, _vp, _vp, _vp],
     "cima_moe_gemm": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -879,22 +879,30 @@ class Kernels:
         self._check(self.lib.cima_rms_mean(yp, wp, len(ys), x.data_ptr(), T, H, eps, int(assign), self._stream()), "rms_mean")
 
     # ------------------------------------------------------------------ routed feed-forward
+    ROUTE_SORT_ROWS = 64        # a step of at most this many rows orders its pairs by expert in the routing launch
+
     def moe_route(self, scores: torch.Tensor, top: int, groups: int, keep: int, scale: float, idx: torch.Tensor,
-                  wgt: torch.Tensor) -> None:
+                  wgt: torch.Tensor, order: bool = False):
         """``scores`` float32 [T, E] holds the router's logits (it is scratch afterwards).  s = sigmoid(logits); the
         experts form ``groups`` equal groups of neighbours, a group's score is the sum of its two best, the best
         ``keep`` groups stay, and the ``top`` best experts among them are chosen: idx [T, top] int32, and their weights
-        s / (sum of the chosen s + 1e-20) * scale in wgt [T, top] float32."""
+        s / (sum of the chosen s + 1e-20) * scale in wgt [T, top] float32.  ``order`` (at most ``ROUTE_SORT_ROWS`` rows): the
+        same launch also orders the pairs by expert; what it returns goes to ``moe_experts`` as ``ordered``."""
         self._need(scores, "scores", torch.float32, 2); self._need(idx, "idx", torch.int32, 2); self._need(wgt, "wgt", torch.float32, 2)
         T, E = scores.shape
         if tuple(idx.shape) != (T, top) or tuple(wgt.shape) != (T, top):
             raise KernelError(f"moe_route: idx {tuple(idx.shape)} / wgt {tuple(wgt.shape)} are not {(T, top)}")
-        if not self._admit("moe_route", T * (E * 8 + top * 8)): return
+        meta = None
+        if order and T <= self.ROUTE_SORT_ROWS:
+            meta = torch.empty(2 * (E + 1) + T * top, dtype=torch.int32, device=scores.device)
+        if not self._admit("moe_route", T * (E * 8 + top * 8)): return meta
+        parts = (meta[:E + 1].data_ptr(), meta[E + 1:2 * (E + 1)].data_ptr(), meta[2 * (E + 1):].data_ptr()) if meta is not None else (None, None, None)
         self._check(self.lib.cima_moe_route(scores.data_ptr(), T, E, top, groups, keep, scale, idx.data_ptr(), wgt.data_ptr(),
-                                            self._stream()), "moe_route")
+                                            *parts, self._stream()), "moe_route")
+        return meta
 
     def moe_experts(self, h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
-                    x: torch.Tensor, act: int = 0, assign: bool = False) -> None:
+                    x: torch.Tensor, act: int = 0, assign: bool = False, ordered: Optional[torch.Tensor] = None) -> None:
         """x[t] += (with ``assign``: =) sum_j wgt[t, j] * W_down[e] (act(W_gate[e] h[t]) * (W_up[e] h[t])), e = idx[t, j], ascending j.
         gate_up [E, 2 ff, H] (an expert's gate rows, then its up rows), down [E, H, ff]; x float32 [T, H].  Four launches:
         the pairs sorted by expert, the two grouped products over tiles of one expert's pairs, the weighted sum.  The
@@ -915,13 +923,13 @@ class Kernels:
         if bf16 and P >= self.MOE_TC_PAIRS:
             return self._moe_experts_tc(h, gate_up, down, idx, wgt, x, act, assign)
         few = bf16 and P <= self.MOE_FEW_PAIRS
-        meta = torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
+        meta = ordered if ordered is not None else torch.empty(2 * (E + 1) + P, dtype=torch.int32, device=dev)
         offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
         z = torch.empty((P, ff), dtype=h.dtype, device=dev)
         y = torch.empty((P, H), dtype=torch.float32, device=dev)
         wb = gate_up.element_size()
         touched = min(E, P)
-        if self._admit("moe_sort", P * 8):
+        if ordered is None and self._admit("moe_sort", P * 8):
             self._check(self.lib.cima_moe_sort(idx.data_ptr(), P, E, offsets.data_ptr(), tiles.data_ptr(), perm.data_ptr(),
                                                self._stream()), "moe_sort")
         name = "moe_few" if few else "moe_gemm"

@@ -106,8 +106,14 @@ class RoutedExperts:
         scores = self.router.logits(h)                                # float32 [rows, E]
         idx = rt.empty(rows, self.top, dtype=torch.int32)
         wgt = rt.empty(rows, self.top, dtype=torch.float32)
-        K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt)
-        K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act, assign=assign)
+        # (a decode step's few rows: the routing launch also orders the pairs by expert)
+        small = rows <= getattr(K_, "ROUTE_SORT_ROWS", 0) and rows * self.top < getattr(K_, "MOE_TC_PAIRS", 0)
+        if small:
+            ordered = K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt, order=True)
+            K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act, assign=assign, ordered=ordered)
+        else:
+            K_.moe_route(scores, self.top, self.groups, self.keep, self.scale, idx, wgt)
+            K_.moe_experts(h, self.gate_up, self.down, idx, wgt, x, self.act, assign=assign)
 
 
 register_feed_forward("moe", RoutedExperts)

@@ -235,10 +235,24 @@ def test_router_choice_and_weights(E, top, groups, keep):
     scores = (h @ wr.T).float().to(DEV)
     idx = torch.empty(T, top, dtype=torch.int32, device=DEV)
     wgt = torch.empty(T, top, dtype=torch.float32, device=DEV)
-    K().moe_route(scores, top, groups, keep, 1.25, idx, wgt)
+    K().moe_route(scores.clone(), top, groups, keep, 1.25, idx, wgt)
     ids, ws = plain_route(h, wr, top, groups, keep, 1.25)
     assert idx.cpu().tolist() == ids
     assert close(wgt, ws, 2e-6)
+    # the same launch can order the pairs by expert (a decode step's few rows)
+    idx2, wgt2 = torch.empty_like(idx), torch.empty_like(wgt)
+    meta = K().moe_route(scores.clone(), top, groups, keep, 1.25, idx2, wgt2, order=True).cpu()
+    assert torch.equal(idx2, idx) and torch.equal(wgt2, wgt)
+    offsets, tiles, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
+    flat = idx.cpu().flatten()
+    assert sorted(perm.tolist()) == list(range(T * top)) and (flat[perm.long()].diff() >= 0).all()
+    assert offsets.tolist() == [int((flat < e).sum()) for e in range(E + 1)]
+    assert tiles.tolist() == [sum(-(-int((flat == j).sum()) // 32) for j in range(e)) for e in range(E + 1)]
+    x1, x2 = torch.zeros(T, H, device=DEV), torch.zeros(T, H, device=DEV)
+    gu, dn = torch.randn(E, 16, H, generator=g).to(DEV), torch.randn(E, H, 8, generator=g).to(DEV)
+    K().moe_experts(h.float().to(DEV), gu, dn, idx, wgt, x1, 0)
+    K().moe_experts(h.float().to(DEV), gu, dn, idx, wgt, x2, 0, ordered=meta.to(DEV))
+    assert torch.equal(x1, x2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
