@@ -69,7 +69,14 @@ __device__ __forceinline__ void moe_route_row(float* scores, float* local, int r
                                               int* idx, float* wgt) {
   float* s = E <= ROUTE_SMEM_EXPERTS ? local + threadIdx.x * (E + 1) : scores + (size_t)row * E;
   const float* z = scores + (size_t)row * E;
-  for (int e = 0; e < E; e++) s[e] = 1.0f / (1.0f + expf(-z[e]));
+  for (int e0 = 0; e0 < E; e0 += 8) {                     // eight logits requested before any is waited for
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) t[j] = e0 + j < E ? z[e0 + j] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (e0 + j < E) s[e0 + j] = 1.0f / (1.0f + expf(-t[j]));
+  }
   const int per = E / groups;
   unsigned long long kept = ~0ull;
   if (keep < groups) {
@@ -94,9 +101,12 @@ __device__ __forceinline__ void moe_route_row(float* scores, float* local, int r
   for (int c = 0; c < top; c++) {
     int best = -1;
     float bs = -1.f;
-    for (int e = 0; e < E; e++) {
-      if (!((kept >> (e / per)) & 1ull)) continue;
-      if (s[e] > bs) { bs = s[e]; best = e; }
+    for (int gi = 0; gi < groups; gi++) {
+      if (!((kept >> gi) & 1ull)) continue;
+      for (int e = gi * per; e < (gi + 1) * per; e++) {
+        const float v = s[e];
+        if (v > bs) { bs = v; best = e; }
+      }
     }
     idx[(size_t)row * top + c] = best;
     wgt[(size_t)row * top + c] = bs;

@@ -199,7 +199,9 @@ int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void
 // Everything of the delta rule that is computed per token before the recurrence, in float32:
 //   qn = q / sqrt(sum q^2 + 1e-6) * dim^(-1/2),  kn = k / sqrt(sum k^2 + 1e-6)            per head of q and k
 //   g  = exp(-exp(A_log[h]) * softplus(a + dt_bias)),  beta = sigmoid(b)
-// One block a row; warp w takes the heads w, w + warps, ... of q and k, then the threads share g and beta.
+// A warp takes one unit of a row: a head of q, a head of k, or a head's decays with its beta; a block four units.  (One
+// block a row, its warps walking the row's units one after another, took 17 us for the 8 rows of a decode step: a chain of
+// some dozen trips to memory on 8 SMs.)
 template <typename TA>
 __global__ void __launch_bounds__(128)
 k_delta_prepare(const TA* __restrict__ qk, int ldqk, const TA* __restrict__ a, int lda, const TA* __restrict__ b, int ldb,
@@ -207,25 +209,47 @@ k_delta_prepare(const TA* __restrict__ qk, int ldqk, const TA* __restrict__ a, i
                 float* __restrict__ g, float* __restrict__ beta, int heads, int kv_heads, int dim) {
   cima_pdl_wait();
   cima_pdl_trigger();        // the next kernel may be set up while this one runs (it waits for this one's end itself)
-  const size_t row = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  const float qscale = 1.0f / sqrtf((float)dim);
-  for (int u = warp; u < 2 * kv_heads; u += nwarp) {           // the heads of q, then those of k
+  const size_t row = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int u = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (u < 2 * kv_heads) {                                       // a head of q (u < kv_heads) or of k
     const TA* src = qk + row * ldqk + (size_t)u * dim;
+    float x[8];                                                 // dim <= 256: eight values a lane
     float ss = 0.f;
-    for (int i = lane; i < dim; i += 32) { const float x = cima_to_f32<TA>(src[i]); ss = fmaf(x, x, ss); }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = lane + 32 * j;
+      x[j] = i < dim ? cima_to_f32<TA>(src[i]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) ss = fmaf(x[j], x[j], ss);
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float r = (1.0f / sqrtf(ss + 1e-6f)) * (u < kv_heads ? qscale : 1.0f);
+    const float r = (1.0f / sqrtf(ss + 1e-6f)) * (u < kv_heads ? 1.0f / sqrtf((float)dim) : 1.0f);
     float* dst = u < kv_heads ? qn + (row * kv_heads + u) * dim : kn + (row * kv_heads + (u - kv_heads)) * dim;
-    for (int i = lane; i < dim; i += 32) dst[i] = cima_to_f32<TA>(src[i]) * r;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = lane + 32 * j;
+      if (i < dim) dst[i] = x[j] * r;
+    }
+  } else if (u < 2 * kv_heads + heads) {                        // a head's decays and its beta
+    const int h = u - 2 * kv_heads;
+    const float rate = expf(A_log[h]);
+    float z[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = lane + 32 * j;
+      z[j] = i < dim ? cima_to_f32<TA>(a[row * lda + (size_t)h * dim + i]) + dt_bias[h * dim + i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = lane + 32 * j;
+      if (i < dim) {
+        const float sp = z[j] > 20.f ? z[j] : log1pf(expf(z[j]));
+        g[(row * heads + h) * dim + i] = expf(-rate * sp);
+      }
+    }
+    if (lane == 0) beta[row * heads + h] = 1.0f / (1.0f + expf(-cima_to_f32<TA>(b[row * ldb + h])));
   }
-  for (int c = threadIdx.x; c < heads * dim; c += blockDim.x) {
-    const float z = cima_to_f32<TA>(a[row * lda + c]) + dt_bias[c];
-    const float sp = z > 20.f ? z : log1pf(expf(z));
-    g[row * heads * dim + c] = expf(-expf(A_log[c / dim]) * sp);
-  }
-  for (int h = threadIdx.x; h < heads; h += blockDim.x)
-    beta[row * heads + h] = 1.0f / (1.0f + expf(-cima_to_f32<TA>(b[row * ldb + h])));
 }
 }  // namespace
 
@@ -260,10 +284,12 @@ extern "C" int cima_delta_prepare(const void* qk, int ldqk, const void* a, int l
                                   const float* A_log, const float* dt_bias, float* qn, float* kn, float* g, float* beta,
                                   int T, int heads, int kv_heads, int dim, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || dim <= 0) return cima_fail(CIMA_E_SIZE, "delta_prepare: heads %d, key heads %d and key size %d must be positive", heads, kv_heads, dim);
+  if (heads <= 0 || kv_heads <= 0 || dim <= 0 || dim > 256) return cima_fail(CIMA_E_SIZE, "delta_prepare: heads %d and key heads %d must be positive, the key size %d in 1..256", heads, kv_heads, dim);
+  if (T > 65535) return cima_fail(CIMA_E_SIZE, "delta_prepare: %d rows exceed one launch; the caller cuts them", T);
+  const dim3 grid((unsigned)((2 * kv_heads + heads + 3) / 4), (unsigned)T);
   int rc;
-  if (dtype == CIMA_F32) rc = cima_launch(k_delta_prepare<float>, dim3(T), dim3(128), (size_t)0, stream, 1, (const float*)qk, ldqk, (const float*)a, lda, (const float*)b, ldb, A_log, dt_bias, qn, kn, g, beta, heads, kv_heads, dim);
-  else if (dtype == CIMA_BF16) rc = cima_launch(k_delta_prepare<__nv_bfloat16>, dim3(T), dim3(128), (size_t)0, stream, 1, (const __nv_bfloat16*)qk, ldqk, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, A_log, dt_bias, qn, kn, g, beta, heads, kv_heads, dim);
+  if (dtype == CIMA_F32) rc = cima_launch(k_delta_prepare<float>, grid, dim3(128), (size_t)0, stream, 1, (const float*)qk, ldqk, (const float*)a, lda, (const float*)b, ldb, A_log, dt_bias, qn, kn, g, beta, heads, kv_heads, dim);
+  else if (dtype == CIMA_BF16) rc = cima_launch(k_delta_prepare<__nv_bfloat16>, grid, dim3(128), (size_t)0, stream, 1, (const __nv_bfloat16*)qk, ldqk, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, A_log, dt_bias, qn, kn, g, beta, heads, kv_heads, dim);
   else return cima_fail(CIMA_E_DTYPE, "delta_prepare: dtype code %d is neither float32 nor bfloat16", dtype);
   return rc ? rc : cima_launch_result();
 }
