@@ -41,7 +41,7 @@ def draw_config(rng: random.Random) -> dict:
             dim = rng.choice([8, 16, 24, 32, 48, 64, 80, 128])
             rotary = None
             if rng.random() < 0.85:
-                dims = rng.choice([d for d in (4, 8, 16, 32, 64, 128) if d <= dim])
+                dims = rng.choice([d for d in (4, 8, 16, 32, 64, 128, dim, dim) if d <= dim])      # a part of the head, or all of it
                 sc = (rng.choice([2.0, 4.0, 8.0]), rng.choice([0.5, 1.0]), rng.choice([2.0, 4.0, 16.0]), rng.choice([16, 64, 512, 4096]))
                 rotary = rot(dims, rng.choice([100.0, 10000.0, 500000.0]), sc if rng.random() < 0.7 else None)
             r_heads = rng.randint(1, 5)
