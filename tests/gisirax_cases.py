@@ -59,7 +59,7 @@ G_A = config(300, 96, 1e-6, 1.3, 2.0, (61, 5, 3), [
     delta(2, 1, 40, 8, 2, 16, 4, moe(56, 4, 1, 0.5))])
 # the layers in another order; one tap (no convolution state); no groups; every expert chosen; no rotation in one layer;
 # a width that is no multiple of 8; one head
-G_B = config(513, 100, 1e-5, 0.6, 5.0, (127, 31, 7), [
+G_B = config(513, 100, 1e-5, 0.6, 5.0, (127, 29, 5), [
     parallel(3, 3, 16, 16, 0.25, None, 1, 8, 8, [0.8], moe(20, 3, 3, 1.5)),
     delta(1, 1, 24, 24, 1, 4, 4, None),
     delta(3, 3, 8, 16, 4, 24, 8, moe(32, 10, 3, 1.25, groups=5, keep=3))])

@@ -47,7 +47,7 @@ def draw_config(rng: random.Random) -> dict:
             r_heads = rng.randint(1, 5)
             layers.append(parallel(heads, kv, dim, rng.choice([8, 16, 24, 32, 48, 64, 96]), rng.choice([0.05, 0.125, 0.25]), rotary,
                                    r_heads, rng.choice([8, 16, 40, 64, 128]), rng.choice([8, 16, 24, 64, 100]),
-                                   [rng.choice([0.3, 0.8, 0.95, 0.99, 0.999]) for _ in range(r_heads)], draw_moe(rng)))
+                                   [rng.choice([0.3, 0.8, 0.95, 0.99, 0.998]) for _ in range(r_heads)], draw_moe(rng)))
         else:
             kv = rng.choice([1, 2, 3])
             layers.append(delta(kv * rng.choice([1, 2, 3]), kv, rng.choice([8, 16, 24, 40, 64, 128, 160]), rng.choice([8, 16, 24, 48, 64, 100]),
